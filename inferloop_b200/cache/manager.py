@@ -4,7 +4,8 @@ group per distinct need, and a slot of fixed-size state per request.
 Layers are sorted into *page groups* by what they need (`PagedKVNeed`: kv heads, head
 size, window).  A group has its own pool, its own block tables and one device tensor
 `[layers_in_group, 2, pages, kv_heads, page_size, head_dim]`; layer l's keys are
-`storage[l, 0]`, its values `storage[l, 1]`.  Pages are taken when the step that first
+`storage[l, 0]`, its values `storage[l, 1]` (a group whose values have another head size
+than its keys keeps them in a tensor of their own, `[layers, pages, kv_heads, page_size, v_head_dim]`).  Pages are taken when the step that first
 touches them is prepared, all groups or none (the reference grows pages per step,
 all-or-nothing: crates/engine/state/src/logical/reservation.rs:106-158), and given back
 when the request ends (crates/engine/runtime/src/pipeline/lifecycle.rs:242-251) or, in a
@@ -54,9 +55,11 @@ class PageGroup:
     page_size: int
     storage: Optional[torch.Tensor] = None
 
+    storage_v: Optional[torch.Tensor] = None      # the values, when their head size is not the keys'
+
     def page_bytes(self, element_size: int) -> int:
-        return (len(self.layers) * 2 * self.need.kv_heads * self.page_size
-                * self.need.head_dim * element_size)
+        return (len(self.layers) * self.need.kv_heads * self.page_size
+                * (self.need.head_dim + self.need.value_dim) * element_size)
 
 
 class CacheManager:
@@ -117,9 +120,14 @@ class CacheManager:
             self.groups.append(PageGroup(gi, need, layers, pool, self.page_size))
         if device is not None:
             for g in self.groups:
+                both = g.need.value_dim == g.need.head_dim
                 g.storage = torch.zeros(
-                    (len(g.layers), 2, g.pool.num_pages, g.need.kv_heads, self.page_size, g.need.head_dim),
+                    (len(g.layers), 2 if both else 1, g.pool.num_pages, g.need.kv_heads, self.page_size, g.need.head_dim),
                     dtype=dtype, device=device)
+                if not both:
+                    g.storage_v = torch.zeros(
+                        (len(g.layers), g.pool.num_pages, g.need.kv_heads, self.page_size, g.need.value_dim),
+                        dtype=dtype, device=device)
         # fixed-size state
         self.slots = SlotPool(max_requests, _handle=self._lib.ilb_ledger_slots(self._h), _ids=self._ids)
         self._slot_state: Dict[Tuple[int, str], torch.Tensor] = {}
@@ -266,8 +274,10 @@ class CacheManager:
         gi = self._group_of_layer.get(owner)
         k = v = None
         if gi is not None and self.groups[gi].storage is not None:
-            s = self.groups[gi].storage[self._index_in_group[owner]]
-            k, v = s[0], s[1]
+            g = self.groups[gi]
+            s = g.storage[self._index_in_group[owner]]
+            k = s[0]
+            v = s[1] if g.storage_v is None else g.storage_v[self._index_in_group[owner]]
         state = {need.name: self._slot_state[(owner, need.name)]
                  for need in self._slot_needs.get(owner, ()) if (owner, need.name) in self._slot_state}
         return LayerCache(owner, gi, self.page_size, k, v, entry.writes_cache, state)
@@ -290,7 +300,7 @@ class CacheManager:
             "live_requests": len(self._live),
             "groups": [{
                 "index": g.index, "layers": list(g.layers), "kv_heads": g.need.kv_heads,
-                "head_dim": g.need.head_dim, "window": g.need.window,
+                "head_dim": g.need.head_dim, "v_head_dim": g.need.value_dim, "window": g.need.window,
                 "total": g.pool.num_pages, "free": g.pool.num_free,
                 "active": g.pool.num_pages - g.pool.num_free,
                 "allocations": g.pool.allocations, "reuses": g.pool.reuses,

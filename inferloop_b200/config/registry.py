@@ -2,8 +2,8 @@
 
 Mirrors the reference's provider registry (crates/model/package/src/providers/
 registry.rs:22-37 hint order, :91-110 duplicate claims rejected, :116-135 resolve):
-hints are collected most specific first -- `architectures`, then `model_type`, then
-the nested `text_config` -- and the first registered entry that claims any of them
+hints are collected most specific first -- `architectures` (or the single name under
+`architecture`), then `model_type`, then the nested `text_config` -- and the first registered entry that claims any of them
 wins.
 """
 from __future__ import annotations
@@ -59,6 +59,11 @@ class ArchitectureRegistry:
                     raise ConfigError(f"architectures must be a list of names, found {names!r}")
                 if name not in out:
                     out.append(name)
+            one = d.get("architecture")            # some formats name their one architecture without a list
+            if one is not None and not isinstance(one, str):
+                raise ConfigError(f"architecture must be a name, found {one!r}")
+            if one is not None and one not in out:
+                out.append(one)
             mt = d.get("model_type")
             if mt is not None and not isinstance(mt, str):
                 raise ConfigError(f"model_type must be a name, found {mt!r}")
@@ -94,7 +99,9 @@ def default_registry() -> ArchitectureRegistry:
     if _DEFAULT is None:
         _DEFAULT = ArchitectureRegistry()
         from ..models.qwen3 import ARCHITECTURE
+        from ..models.sufolix import ARCHITECTURE as SUFOLIX
         _DEFAULT.register(ARCHITECTURE)
+        _DEFAULT.register(SUFOLIX)
     return _DEFAULT
 
 

@@ -55,7 +55,7 @@ class LayerSpec:
     prefix: str                 # e.g. "model.layers.3."
     block: PartSpec             # arrangement of the parts, e.g. kind "pre_norm"
     mixer: PartSpec             # token mixer, e.g. kind "gqa_attention"
-    feed_forward: PartSpec      # e.g. kind "swiglu"
+    feed_forward: PartSpec      # e.g. kind "swiglu"; kind "none" for a layer that has only its mixer
     norm: PartSpec              # norm used by the block, e.g. kind "rms"
 
 
@@ -96,8 +96,14 @@ class ModelSpec:
     # with several axes, say.  Steps carry them (StepEntry.extras); parts read
     # step.extras[name] as an int32 [tokens, width] device tensor.
     token_extras: Tuple[Tuple[str, int], ...] = ()
+    # Copies of the residual stream that the blocks keep per token (hyper-connections).  The
+    # embedding fills all of them, the blocks see [tokens, residual_streams * hidden_size], and
+    # their sum is what the final norm reads.
+    residual_streams: int = 1
 
     def __post_init__(self) -> None:
+        if self.residual_streams < 1:
+            raise ValueError("a model has at least one residual stream")
         if not self.run_order:
             object.__setattr__(
                 self, "run_order",

@@ -7,6 +7,9 @@
 // the block's warps depends on lo and p alone, so the result at a position never depends
 // on what else is in the batch or on how the tokens were cut into steps.
 //
+// Keys and queries have head size d, values and the output dv (the V cache is
+// [pages, nkv, page_size, dv]).
+//
 // Reference formula: s_j = q.k_j / sqrt(d), p = softmax(s), o = sum p_j v_j, query head h
 // uses kv head h / (nq / nkv); window start (p + 1).saturating_sub(w)
 // (crates/testing/cpu/reference-ops/src/kernels.rs:251-297).
@@ -24,7 +27,7 @@ paged_attention_simple_kernel(const TQ* __restrict__ q, TQ* __restrict__ out,
                               const TC* __restrict__ k_cache, const TC* __restrict__ v_cache,
                               const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                               const int* __restrict__ block_table, int max_blocks, int page_size,
-                              int num_pages, int window, float scale, int nq, int nkv, int d,
+                              int num_pages, int window, float scale, int nq, int nkv, int d, int dv,
                               int q_stride, int out_stride) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
@@ -76,11 +79,11 @@ paged_attention_simple_kernel(const TQ* __restrict__ q, TQ* __restrict__ out,
       const int key = lo + tile * 32 + jj;
       const int page = table[key / page_size];
       if (page < 0 || page >= num_pages) continue;
-      const TC* vr = v_cache + (((size_t)page * nkv + kvh) * page_size + (key % page_size)) * d;
+      const TC* vr = v_cache + (((size_t)page * nkv + kvh) * page_size + (key % page_size)) * dv;
 #pragma unroll
       for (int i = 0; i < R; ++i) {
         const int c = lane + 32 * i;
-        if (c < d) acc[i] = fmaf(w, to_float(vr[c]), acc[i]);
+        if (c < dv) acc[i] = fmaf(w, to_float(vr[c]), acc[i]);
       }
     }
   }
@@ -88,7 +91,7 @@ paged_attention_simple_kernel(const TQ* __restrict__ q, TQ* __restrict__ out,
 #pragma unroll
   for (int i = 0; i < R; ++i) {
     const int c = lane + 32 * i;
-    if (c < d) red_acc[warp][c] = acc[i];
+    if (c < dv) red_acc[warp][c] = acc[i];
   }
   __syncthreads();
   float m_all = -INFINITY;
@@ -98,33 +101,33 @@ paged_attention_simple_kernel(const TQ* __restrict__ q, TQ* __restrict__ out,
     f[w] = (red_m[w] == -INFINITY) ? 0.f : expf(red_m[w] - m_all);
     l_all += red_l[w] * f[w];
   }
-  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+  for (int c = threadIdx.x; c < dv; c += blockDim.x) {
     float o = 0.f;
     for (int w = 0; w < kWarps; ++w) o += red_acc[w][c] * f[w];
     // A row whose keys are all unreachable gives 0, as the reference does
     // (crates/backend/cuda-kernels/src/tile/attention/resident_attention_prefill_kernels.rs:460-468).
-    out[(size_t)t * out_stride + (size_t)h * d + c] = from_float<TQ>(l_all > 0.f ? o / l_all : 0.f);
+    out[(size_t)t * out_stride + (size_t)h * dv + c] = from_float<TQ>(l_all > 0.f ? o / l_all : 0.f);
   }
 }
 
 ILB_EXPORT int ilb_paged_attention_simple(
     const void* q, void* out, int dtype, const void* k_cache, const void* v_cache, int cache_dtype,
     const int* positions, const int* seq_of_token, const int* block_table, int max_blocks,
-    int page_size, int num_pages, int window, float scale, int n_tokens, int nq, int nkv, int d,
+    int page_size, int num_pages, int window, float scale, int n_tokens, int nq, int nkv, int d, int dv,
     int q_stride, int out_stride, cudaStream_t stream) {
   ILB_REQUIRE(n_tokens >= 0 && nq > 0 && nkv > 0 && d > 0, "attention: bad sizes");
   ILB_REQUIRE(nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
-  ILB_REQUIRE(d <= kMaxHeadDim, "attention: head size %d exceeds %d", d, kMaxHeadDim);
+  ILB_REQUIRE(dv > 0 && d <= kMaxHeadDim && dv <= kMaxHeadDim, "attention: head size %d / %d exceeds %d", d, dv, kMaxHeadDim);
   ILB_REQUIRE(nq <= 65535, "attention: too many heads");
   ILB_REQUIRE(page_size > 0 && max_blocks > 0 && num_pages > 0, "attention: bad cache geometry");
   ILB_REQUIRE(window >= 0, "attention: negative window");
-  ILB_REQUIRE(q_stride >= nq * d && out_stride >= nq * d, "attention: strides too small");
+  ILB_REQUIRE(q_stride >= nq * d && out_stride >= nq * dv, "attention: strides too small");
   if (n_tokens == 0) return 0;
   dim3 grid(n_tokens, nq);
 #define ILB_LAUNCH(TQ, TC)                                                                    \
   ilb::launch(paged_attention_simple_kernel<TQ, TC>, dim3(grid), dim3(kWarps * 32), 0, stream,                      \
       (const TQ*)q, (TQ*)out, (const TC*)k_cache, (const TC*)v_cache, positions, seq_of_token, \
-      block_table, max_blocks, page_size, num_pages, window, scale, nq, nkv, d, q_stride,      \
+      block_table, max_blocks, page_size, num_pages, window, scale, nq, nkv, d, dv, q_stride,  \
       out_stride)
   if (dtype == kF32 && cache_dtype == kF32) ILB_LAUNCH(float, float);
   else if (dtype == kBF16 && cache_dtype == kBF16) ILB_LAUNCH(__nv_bfloat16, __nv_bfloat16);

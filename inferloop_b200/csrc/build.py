@@ -38,6 +38,8 @@ MODULES: Dict[str, List[str]] = {
     "attention_tc": [],
     "attention_decode": [],
     "sampling": [],
+    "hyper": [],
+    "moe": [],
 }
 
 _LOCK = threading.Lock()

@@ -13,27 +13,32 @@ using namespace ilb;
 // ---------------------------------------------------------------- embedding gather
 template <typename TT>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TT* __restrict__ table,
-                             float* __restrict__ out, int hidden, int vocab) {
+                             float* __restrict__ out, int hidden, int vocab, float scale, int streams) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
   const int t = blockIdx.x;
   const int tok = tokens[t];
   const bool ok = tok >= 0 && tok < vocab;
   const TT* row = table + (size_t)(ok ? tok : 0) * hidden;
-  float* o = out + (size_t)t * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = ok ? to_float(row[i]) : 0.f;
+  float* o = out + (size_t)t * hidden * streams;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = ok ? to_float(row[i]) * scale : 0.f;
+    for (int s = 0; s < streams; ++s) o[(size_t)s * hidden + i] = v;
+  }
 }
 
+// out[t, s, :] = table[tokens[t], :] * scale for every one of `streams` copies of the
+// residual stream (streams = 1, scale = 1: the plain gather).
 ILB_EXPORT int ilb_embed(const int* tokens, const void* table, int table_dtype, float* out,
-                         int n_tokens, int hidden, int vocab, cudaStream_t stream) {
-  ILB_REQUIRE(n_tokens >= 0 && hidden > 0 && vocab > 0, "embed: bad sizes T=%d H=%d V=%d",
-              n_tokens, hidden, vocab);
+                         int n_tokens, int hidden, int vocab, float scale, int streams, cudaStream_t stream) {
+  ILB_REQUIRE(n_tokens >= 0 && hidden > 0 && vocab > 0 && streams > 0, "embed: bad sizes T=%d H=%d V=%d streams=%d",
+              n_tokens, hidden, vocab, streams);
   if (n_tokens == 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == kF32)
-    ilb::launch(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const float*)table, out, hidden, vocab);
+    ilb::launch(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const float*)table, out, hidden, vocab, scale, streams);
   else if (table_dtype == kBF16)
-    ilb::launch(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const __nv_bfloat16*)table, out, hidden, vocab);
+    ilb::launch(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const __nv_bfloat16*)table, out, hidden, vocab, scale, streams);
   else
     return fail("embed: unknown table dtype %d", table_dtype);
   return check_launch("embed");
@@ -209,20 +214,29 @@ ILB_EXPORT int ilb_silu_mul(const void* in, void* out, int dtype, int rows, int 
 
 // ---------------------------------------------------------------- row gather
 __global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ idx,
-                                   float* __restrict__ out, int width, int n_rows_in) {
+                                   float* __restrict__ out, int width, int n_rows_in, int streams) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
   const int r = idx[blockIdx.x];
   const bool ok = r >= 0 && r < n_rows_in;
-  for (int i = threadIdx.x; i < width; i += blockDim.x)
-    out[(size_t)blockIdx.x * width + i] = ok ? x[(size_t)r * width + i] : 0.f;
+  const float* row = x + (size_t)(ok ? r : 0) * width * streams;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float v = 0.f;
+    if (ok) {
+      v = row[i];
+      for (int s = 1; s < streams; ++s) v += row[(size_t)s * width + i];
+    }
+    out[(size_t)blockIdx.x * width + i] = v;
+  }
 }
 
+// out[r, :] = sum over the `streams` copies of row idx[r] of x[rows, streams, width], added in
+// stream order (streams = 1: the plain gather).
 ILB_EXPORT int ilb_gather_rows(const float* x, const int* idx, float* out, int n_out, int width,
-                               int n_rows_in, cudaStream_t stream) {
-  ILB_REQUIRE(n_out >= 0 && width > 0, "gather_rows: bad sizes");
+                               int n_rows_in, int streams, cudaStream_t stream) {
+  ILB_REQUIRE(n_out >= 0 && width > 0 && streams > 0, "gather_rows: bad sizes");
   if (n_out == 0) return 0;
-  ilb::launch(gather_rows_kernel, dim3(n_out), dim3(256), 0, stream, x, idx, out, width, n_rows_in);
+  ilb::launch(gather_rows_kernel, dim3(n_out), dim3(256), 0, stream, x, idx, out, width, n_rows_in, streams);
   return check_launch("gather_rows");
 }
 

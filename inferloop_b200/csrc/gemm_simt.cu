@@ -19,9 +19,14 @@ template <typename TA, typename TO, int BM, int BN, int TM, int TN>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_simt_kernel(const TA* __restrict__ A, const TA* __restrict__ W,
                  const float* __restrict__ bias, TO* __restrict__ out, int M, int N, int K,
-                 int lda, int ldw, int ldo, int accumulate) {
+                 int lda, int ldw, int ldo, int accumulate, const int* __restrict__ block_group, long long group_stride) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
+  if (block_group != nullptr) {                      // this block of rows multiplies its own group's matrix
+    const int g = block_group[blockIdx.y];
+    if (g < 0) return;
+    W += (size_t)g * group_stride;
+  }
   constexpr int BK = 16;
   constexpr int THREADS = (BM / TM) * (BN / TN);
   __shared__ float As[BK][BM + 1];
@@ -123,9 +128,14 @@ template <typename TA, typename TO, int BM, int BN, int TM, int TN, int PF>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_simt_fast_kernel(const TA* __restrict__ A, const TA* __restrict__ W,
                       const float* __restrict__ bias, TO* __restrict__ out, int M, int N, int K,
-                      int lda, int ldw, int ldo, int accumulate) {
+                      int lda, int ldw, int ldo, int accumulate, const int* __restrict__ block_group, long long group_stride) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
+  if (block_group != nullptr) {                      // this block of rows multiplies its own group's matrix
+    const int g = block_group[blockIdx.y];
+    if (g < 0) return;
+    W += (size_t)g * group_stride;
+  }
   constexpr int BK = 16;                             // K block; PF blocks are held in registers ahead of the one in shared memory
   static_assert(PF % 2 == 0, "the shared-memory buffer of a block follows from its register slot");
   constexpr int THREADS = (BM / TM) * (BN / TN);
@@ -243,29 +253,31 @@ gemm_simt_fast_kernel(const TA* __restrict__ A, const TA* __restrict__ W,
 
 template <typename TA, typename TO>
 static int launch(const void* A, const void* W, const float* bias, void* out, int M, int N, int K,
-                  int lda, int ldw, int ldo, int accumulate, cudaStream_t stream) {
+                  int lda, int ldw, int ldo, int accumulate, cudaStream_t stream,
+                  const int* block_group = nullptr, long long group_stride = 0) {
   const bool pieces = K % 4 == 0 && lda % 4 == 0 && ldw % 4 == 0 &&
                       (uintptr_t)A % (4 * sizeof(TA)) == 0 && (uintptr_t)W % (4 * sizeof(TA)) == 0;
-  if (pieces && M <= 16) {
+  const bool grouped = block_group != nullptr;       // groups are dealt in blocks of kGroupRows rows: the 16-row tiles
+  if (pieces && (M <= 16 || grouped)) {
     constexpr int BM = 16, BN = 64, TM = 4, TN = 2;            // 4 warps, one per group of rows ty, ty + 4, ty + 8, ty + 12
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     ilb::launch(gemm_simt_fast_kernel<TA, TO, BM, BN, TM, TN, 8>, dim3(grid), dim3((BM / TM) * (BN / TN)), 0, stream,
-        (const TA*)A, (const TA*)W, bias, (TO*)out, M, N, K, lda, ldw, ldo, accumulate);
+        (const TA*)A, (const TA*)W, bias, (TO*)out, M, N, K, lda, ldw, ldo, accumulate, block_group, group_stride);
   } else if (pieces) {
     constexpr int BM = 128, BN = 128, TM = 8, TN = 8;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     ilb::launch(gemm_simt_fast_kernel<TA, TO, BM, BN, TM, TN, 2>, dim3(grid), dim3((BM / TM) * (BN / TN)), 0, stream,
-        (const TA*)A, (const TA*)W, bias, (TO*)out, M, N, K, lda, ldw, ldo, accumulate);
-  } else if (M <= 16) {
+        (const TA*)A, (const TA*)W, bias, (TO*)out, M, N, K, lda, ldw, ldo, accumulate, block_group, group_stride);
+  } else if (M <= 16 || grouped) {
     constexpr int BM = 16, BN = 32, TM = 2, TN = 2;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     ilb::launch(gemm_simt_kernel<TA, TO, BM, BN, TM, TN>, dim3(grid), dim3((BM / TM) * (BN / TN)), 0, stream, 
-        (const TA*)A, (const TA*)W, bias, (TO*)out, M, N, K, lda, ldw, ldo, accumulate);
+        (const TA*)A, (const TA*)W, bias, (TO*)out, M, N, K, lda, ldw, ldo, accumulate, block_group, group_stride);
   } else {
     constexpr int BM = 64, BN = 64, TM = 4, TN = 4;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     ilb::launch(gemm_simt_kernel<TA, TO, BM, BN, TM, TN>, dim3(grid), dim3((BM / TM) * (BN / TN)), 0, stream, 
-        (const TA*)A, (const TA*)W, bias, (TO*)out, M, N, K, lda, ldw, ldo, accumulate);
+        (const TA*)A, (const TA*)W, bias, (TO*)out, M, N, K, lda, ldw, ldo, accumulate, block_group, group_stride);
   }
   return check_launch("gemm_simt");
 }
@@ -287,6 +299,29 @@ ILB_EXPORT int ilb_gemm_simt(const void* A, const void* W, const float* bias, vo
   if (in_dtype == kBF16 && out_dtype == kBF16)
     return launch<__nv_bfloat16, __nv_bfloat16>(A, W, bias, out, M, N, K, lda, ldw, ldo, accumulate, stream);
   return fail("gemm_simt: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
+}
+
+// The same product for rows that are dealt to groups in blocks of 16 (ilb_gemm_simt_group_rows):
+// block b of A (rows 16 b .. 16 b + 15) is multiplied by the matrix W + block_group[b] *
+// group_stride elements, and left alone when block_group[b] < 0.  M is the number of rows that
+// the blocks cover.  This is how a routed feed-forward runs its experts over rows sorted by expert.
+ILB_EXPORT int ilb_gemm_simt_group_rows() { return 16; }
+
+ILB_EXPORT int ilb_gemm_simt_grouped(const void* A, const void* W, void* out, int in_dtype, int out_dtype, int M, int N,
+                                     int K, int lda, int ldw, int ldo, const int* block_group, long long group_stride,
+                                     cudaStream_t stream) {
+  ILB_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_simt_grouped: bad sizes M=%d N=%d K=%d", M, N, K);
+  ILB_REQUIRE(lda >= K && ldw >= K && ldo >= N, "gemm_simt_grouped: leading dimensions too small");
+  ILB_REQUIRE(block_group != nullptr && group_stride >= 0, "gemm_simt_grouped: needs the group of every block of rows");
+  ILB_REQUIRE(M % 16 == 0 && M / 16 <= 65535, "gemm_simt_grouped: rows must come in blocks of 16 (at most 65535 blocks), found M=%d", M);
+  if (M == 0) return 0;
+  if (in_dtype == kF32 && out_dtype == kF32)
+    return launch<float, float>(A, W, nullptr, out, M, N, K, lda, ldw, ldo, 0, stream, block_group, group_stride);
+  if (in_dtype == kBF16 && out_dtype == kF32)
+    return launch<__nv_bfloat16, float>(A, W, nullptr, out, M, N, K, lda, ldw, ldo, 0, stream, block_group, group_stride);
+  if (in_dtype == kBF16 && out_dtype == kBF16)
+    return launch<__nv_bfloat16, __nv_bfloat16>(A, W, nullptr, out, M, N, K, lda, ldw, ldo, 0, stream, block_group, group_stride);
+  return fail("gemm_simt_grouped: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
 }
 
 ILB_DEFINE_LAST_ERROR()

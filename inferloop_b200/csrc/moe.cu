@@ -1,0 +1,246 @@
+// Routed feed-forward ("mixture of experts"): what lies around the experts' matrix products.
+//
+//   route    router logits z[T, E] (32-bit) -> scores (sigmoid of each logit, or softmax over the
+//            experts), the `top` best experts of every token (ties to the lower index) and their
+//            weights (the chosen scores, optionally divided by their sum)
+//   plan     the (token, choice) pairs sorted by expert: every expert's rows start at a multiple
+//            of `block_rows`, so that a block of rows belongs to one expert; pos[pair] = row,
+//            row_pair[row] = pair or -1, block_expert[block] = expert or -1
+//   gather   a[row, :] = x[token of the row's pair, :] (times the pair's weight, when the weight
+//            multiplies the expert's input), zero for rows that hold no pair
+//   combine  y[t, :] += sum over the token's choices, in choice order, of (weight *) out[pos, :]
+//            (+ gate[t] * shared[t, :], gate = sigmoid of a logit, for an expert every token uses)
+//
+// Scores, weights and the sums are 32-bit.  Nothing here depends on the host knowing how many
+// tokens an expert got: every size is the worst case, and blocks without an expert are skipped,
+// so a recorded launch sequence can be replayed for another batch.
+#include <math.h>
+#include "common.cuh"
+
+using namespace ilb;
+
+constexpr int kMaxExpertsPerLane = 16;      // experts <= 32 * this
+constexpr int kMaxTop = 32;
+
+__device__ __forceinline__ float sigmoid_stable(float x) {
+  if (x >= 0.f) return 1.0f / (1.0f + expf(-x));
+  const float e = expf(x);
+  return e / (1.0f + e);
+}
+
+// One warp per token.
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ logits, int ld, int n_tokens, int experts, int top, int softmax,
+                 int renormalize, int* __restrict__ choice, float* __restrict__ weight) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= n_tokens) return;
+  const float* z = logits + (size_t)t * ld;
+  float s[kMaxExpertsPerLane];
+  float zmax = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+    const int e = lane + 32 * i;
+    s[i] = e < experts ? z[e] : -INFINITY;
+    zmax = fmaxf(zmax, s[i]);
+  }
+  if (softmax) {
+    zmax = warp_max(zmax);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+      const int e = lane + 32 * i;
+      s[i] = e < experts ? expf(s[i] - zmax) : -INFINITY;
+      if (e < experts) sum += s[i];
+    }
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i)
+      if (lane + 32 * i < experts) s[i] = s[i] / sum;
+  } else {
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i)
+      if (lane + 32 * i < experts) s[i] = sigmoid_stable(s[i]);
+  }
+  float chosen_w = 0.f, total = 0.f;     // lane j keeps the j-th choice
+  int chosen_e = 0;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+      const int e = lane + 32 * i;
+      if (e < experts && (s[i] > best || (s[i] == best && e < best_e)) && s[i] != -INFINITY) { best = s[i]; best_e = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+    }
+    if (best_e == 0x7fffffff) { best_e = 0; best = 0.f; }      // (non-finite logits: keep the indices in range)
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i)
+      if (lane + 32 * i == best_e) s[i] = -INFINITY;            // taken
+    if (lane == j) { chosen_w = best; chosen_e = best_e; }
+    total += best;
+  }
+  if (lane < top) {
+    choice[(size_t)t * top + lane] = chosen_e;
+    weight[(size_t)t * top + lane] = renormalize ? chosen_w / total : chosen_w;
+  }
+}
+
+ILB_EXPORT int ilb_moe_max_experts() { return 32 * kMaxExpertsPerLane; }
+ILB_EXPORT int ilb_moe_max_top() { return kMaxTop; }
+
+// logits: [T, ld] 32-bit, the first `experts` columns are the router's.  choice / weight: [T, top].
+ILB_EXPORT int ilb_moe_route(const float* logits, int ld, int n_tokens, int experts, int top, int softmax, int renormalize,
+                             int* choice, float* weight, cudaStream_t stream) {
+  ILB_REQUIRE(n_tokens >= 0 && experts > 0 && experts <= 32 * kMaxExpertsPerLane, "moe_route: %d experts (at most %d)", experts,
+              32 * kMaxExpertsPerLane);
+  ILB_REQUIRE(top > 0 && top <= experts && top <= kMaxTop, "moe_route: top %d of %d experts (at most %d)", top, experts, kMaxTop);
+  ILB_REQUIRE(ld >= experts, "moe_route: row stride too small");
+  if (n_tokens == 0) return 0;
+  ilb::launch(moe_route_kernel, dim3((n_tokens + 3) / 4), dim3(128), 0, stream, logits, ld, n_tokens, experts, top, softmax,
+              renormalize, choice, weight);
+  return check_launch("moe_route");
+}
+
+// One CTA.  counts and offsets of the experts live in shared memory.
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* __restrict__ choice, int n_pairs, int experts, int block_rows, int max_rows,
+                int* __restrict__ pos, int* __restrict__ row_pair, int* __restrict__ block_expert) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  extern __shared__ int sh[];
+  int* count = sh;                 // [experts]
+  int* start = sh + experts;       // [experts + 1], in rows
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+  for (int r = threadIdx.x; r < max_rows; r += blockDim.x) row_pair[r] = -1;
+  for (int b = threadIdx.x; b < max_rows / block_rows; b += blockDim.x) block_expert[b] = -1;
+  __syncthreads();
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+    const int e = choice[p];
+    pos[p] = (e >= 0 && e < experts) ? atomicAdd(&count[e], 1) : -1;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < experts; ++e) {
+      start[e] = at;
+      at += (count[e] + block_rows - 1) / block_rows * block_rows;
+    }
+    start[experts] = at;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x)
+    for (int b = start[e] / block_rows; b < start[e + 1] / block_rows; ++b) block_expert[b] = e;
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+    const int e = choice[p];
+    if (pos[p] < 0) continue;
+    const int row = start[e] + pos[p];
+    pos[p] = row;
+    row_pair[row] = p;
+  }
+}
+
+// Rows that n_pairs pairs over `experts` experts can need when every expert's rows are padded to
+// a multiple of block_rows.
+static inline long long plan_rows(long long n_pairs, int experts, int block_rows) {
+  const long long most_experts = n_pairs < experts ? n_pairs : experts;
+  const long long rows = n_pairs + most_experts * (block_rows - 1);
+  return (rows + block_rows - 1) / block_rows * block_rows;
+}
+ILB_EXPORT long long ilb_moe_plan_rows(long long n_pairs, int experts, int block_rows) { return plan_rows(n_pairs, experts, block_rows); }
+
+// choice: [n_pairs]; pos: [n_pairs]; row_pair: [max_rows]; block_expert: [max_rows / block_rows];
+// max_rows >= ilb_moe_plan_rows(n_pairs, experts, block_rows), a multiple of block_rows.
+ILB_EXPORT int ilb_moe_plan(const int* choice, int n_pairs, int experts, int block_rows, int max_rows, int* pos, int* row_pair,
+                            int* block_expert, cudaStream_t stream) {
+  ILB_REQUIRE(n_pairs >= 0 && experts > 0 && block_rows > 0, "moe_plan: bad sizes");
+  ILB_REQUIRE(max_rows % block_rows == 0 && max_rows >= plan_rows(n_pairs, experts, block_rows), "moe_plan: %d rows are too few",
+              max_rows);
+  ILB_REQUIRE((size_t)(2 * experts + 1) * sizeof(int) <= 48 * 1024, "moe_plan: too many experts");
+  if (n_pairs == 0) return 0;
+  ilb::launch(moe_plan_kernel, dim3(1), dim3(1024), (size_t)(2 * experts + 1) * sizeof(int), stream, choice, n_pairs, experts,
+              block_rows, max_rows, pos, row_pair, block_expert);
+  return check_launch("moe_plan");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_gather_kernel(const T* __restrict__ x, const float* __restrict__ weight, const int* __restrict__ row_pair, int top, int width,
+                  T* __restrict__ out) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  const int row = blockIdx.x;
+  const int p = row_pair[row];
+  T* o = out + (size_t)row * width;
+  if (p < 0) {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_float<T>(0.f);
+    return;
+  }
+  const T* src = x + (size_t)(p / top) * width;
+  if (weight == nullptr) {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = src[i];
+  } else {
+    const float w = weight[p];
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_float<T>(w * to_float(src[i]));
+  }
+}
+
+// x: [T, width]; out: [rows, width]; weight (may be null): [n_pairs].
+ILB_EXPORT int ilb_moe_gather(const void* x, int dtype, const float* weight, const int* row_pair, int rows, int top, int width,
+                              void* out, cudaStream_t stream) {
+  ILB_REQUIRE(rows >= 0 && top > 0 && width > 0, "moe_gather: bad sizes");
+  if (rows == 0) return 0;
+  if (dtype == kF32)
+    ilb::launch(moe_gather_kernel<float>, dim3(rows), dim3(128), 0, stream, (const float*)x, weight, row_pair, top, width, (float*)out);
+  else if (dtype == kBF16)
+    ilb::launch(moe_gather_kernel<__nv_bfloat16>, dim3(rows), dim3(128), 0, stream, (const __nv_bfloat16*)x, weight, row_pair, top,
+                width, (__nv_bfloat16*)out);
+  else
+    return fail("moe_gather: unknown dtype %d", dtype);
+  return check_launch("moe_gather");
+}
+
+__global__ void __launch_bounds__(128)
+moe_combine_kernel(const float* __restrict__ routed, const int* __restrict__ pos, const float* __restrict__ weight, int top,
+                   const float* __restrict__ shared, const float* __restrict__ gate_logit, int gate_ld, int width,
+                   float* __restrict__ y) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  const int t = blockIdx.x;
+  __shared__ int rows[kMaxTop];
+  __shared__ float ws[kMaxTop];
+  if (threadIdx.x < top) {
+    rows[threadIdx.x] = pos[(size_t)t * top + threadIdx.x];
+    ws[threadIdx.x] = weight != nullptr ? weight[(size_t)t * top + threadIdx.x] : 1.0f;
+  }
+  __syncthreads();
+  float gate = 1.0f;
+  if (shared != nullptr && gate_logit != nullptr) gate = sigmoid_stable(gate_logit[(size_t)t * gate_ld]);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float v = 0.f;
+    for (int j = 0; j < top; ++j)
+      if (rows[j] >= 0) v = fmaf(ws[j], routed[(size_t)rows[j] * width + i], v);
+    if (shared != nullptr) v = fmaf(gate, shared[(size_t)t * width + i], v);
+    y[(size_t)t * width + i] += v;
+  }
+}
+
+// routed: [rows, width] 32-bit, the experts' outputs; pos: [T, top]; weight: [T, top] or null
+// (the weight was applied to the input); shared: [T, width] 32-bit or null; gate_logit: a column
+// of a 32-bit matrix with row stride gate_ld, or null (no gate); y: [T, width] 32-bit, added to.
+ILB_EXPORT int ilb_moe_combine(const float* routed, const int* pos, const float* weight, int top, const float* shared,
+                               const float* gate_logit, int gate_ld, int n_tokens, int width, float* y, cudaStream_t stream) {
+  ILB_REQUIRE(n_tokens >= 0 && top > 0 && top <= kMaxTop && width > 0, "moe_combine: bad sizes");
+  if (n_tokens == 0) return 0;
+  ilb::launch(moe_combine_kernel, dim3(n_tokens), dim3(128), 0, stream, routed, pos, weight, top, shared, gate_logit, gate_ld, width, y);
+  return check_launch("moe_combine");
+}
+
+ILB_DEFINE_LAST_ERROR()

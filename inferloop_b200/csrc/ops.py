@@ -93,14 +93,15 @@ def _f(v) -> ctypes.c_float:
 
 
 # --------------------------------------------------------------------------- rows
-def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, :] = table[tokens[t], :] widened to 32-bit."""
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float = 1.0, streams: int = 1) -> None:
+    """out[t, s, :] = table[tokens[t], :] * scale, widened to 32-bit, for each of `streams`
+    copies of the residual stream (out is [T, streams * H])."""
     _need(tokens, "embed tokens", torch.int32); _need(table, "embed table"); _need(out, "embed out", torch.float32)
-    T, H = out.shape
-    if tokens.numel() != T or table.shape[1] != H:
+    T, H = out.shape[0], table.shape[1]
+    if tokens.numel() != T or out.shape[1] != H * streams:
         raise KernelError("embed: shapes do not agree")
     _call("elementwise", "ilb_embed", _ptr(tokens), _ptr(table), _i(_code(table)), _ptr(out),
-          _i(T), _i(H), _i(table.shape[0]), _stream(out))
+          _i(T), _i(H), _i(table.shape[0]), _f(scale), _i(streams), _stream(out))
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
@@ -124,12 +125,121 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
           _i(width), _i(gate_up.shape[1]), _stream(out))
 
 
-def gather_rows(x: torch.Tensor, index: torch.Tensor, out: torch.Tensor) -> None:
+def gather_rows(x: torch.Tensor, index: torch.Tensor, out: torch.Tensor, streams: int = 1) -> None:
+    """out[r, :] = the sum of the `streams` copies of row index[r] of x [rows, streams * width]."""
     _need(x, "gather x", torch.float32); _need(index, "gather index", torch.int32); _need(out, "gather out", torch.float32)
-    if out.shape[0] != index.numel() or out.shape[1] != x.shape[1]:
+    if out.shape[0] != index.numel() or out.shape[1] * streams != x.shape[1]:
         raise KernelError("gather_rows: shapes do not agree")
     _call("elementwise", "ilb_gather_rows", _ptr(x), _ptr(index), _ptr(out), _i(out.shape[0]),
-          _i(x.shape[1]), _i(x.shape[0]), _stream(x))
+          _i(out.shape[1]), _i(x.shape[0]), _i(streams), _stream(x))
+
+
+# --------------------------------------------------------------------------- several residual streams
+def streams_read(x: torch.Tensor, coef: torch.Tensor, streams: int, norm_weight: Optional[torch.Tensor] = None,
+                 eps: float = 0.0, normed: Optional[torch.Tensor] = None, u_out: Optional[torch.Tensor] = None,
+                 y_zero: Optional[torch.Tensor] = None) -> None:
+    """u = sum_s coef[s] x[:, s, :] of x [T, streams * H] (32-bit); `normed` = RMS norm of u with
+    `norm_weight` (any compute dtype), `u_out` = u, `y_zero` is set to zero (see hyper.cu)."""
+    _need(x, "streams x", torch.float32); _need(coef, "streams coefficients", torch.float32)
+    _need(norm_weight, "streams norm weight", torch.float32); _need(normed, "streams normed")
+    _need(u_out, "streams u", torch.float32); _need(y_zero, "streams y", torch.float32)
+    T, H = x.shape[0], x.shape[1] // streams
+    if x.shape[1] != H * streams or coef.numel() != streams or (norm_weight is not None and norm_weight.numel() != H):
+        raise KernelError("streams_read: shapes do not agree")
+    for t in (normed, u_out, y_zero):
+        if t is not None and tuple(t.shape) != (T, H):
+            raise KernelError("streams_read: outputs must be [tokens, width]")
+    _call("hyper", "ilb_streams_read", _ptr(x), _ptr(coef), _ptr(norm_weight), _ptr(normed),
+          _i(_code(normed) if normed is not None else F32), _ptr(u_out), _ptr(y_zero), _i(T), _i(H), _i(streams), _f(eps),
+          _stream(x))
+
+
+def streams_write(x: torch.Tensor, y: torch.Tensor, mix: torch.Tensor, out_coef: torch.Tensor, streams: int) -> None:
+    """In place on x [T, streams * H]: x[:, t, :] = sum_s mix[s, t] x[:, s, :] + out_coef[t] * y."""
+    _need(x, "streams x", torch.float32); _need(y, "streams y", torch.float32)
+    _need(mix, "streams mix", torch.float32); _need(out_coef, "streams out", torch.float32)
+    T, H = y.shape
+    if tuple(x.shape) != (T, H * streams) or mix.numel() != streams * streams or out_coef.numel() != streams:
+        raise KernelError("streams_write: shapes do not agree")
+    _call("hyper", "ilb_streams_write", _ptr(x), _ptr(y), _ptr(mix), _ptr(out_coef), _i(T), _i(H), _i(streams), _stream(x))
+
+
+# --------------------------------------------------------------------------- routed feed-forward
+def moe_limits() -> tuple:
+    """(most experts, most experts per token) the routing kernels take."""
+    lib = load_module("moe")
+    return int(lib.ilb_moe_max_experts()), int(lib.ilb_moe_max_top())
+
+
+def moe_plan_rows(n_pairs: int, experts: int, block_rows: int) -> int:
+    """Rows that `n_pairs` (token, expert) pairs need once every expert's rows start at a
+    multiple of `block_rows` (the worst case over all routings)."""
+    most = min(n_pairs, experts)
+    rows = n_pairs + most * (block_rows - 1)
+    return -(-rows // block_rows) * block_rows
+
+
+def moe_route(logits: torch.Tensor, experts: int, top: int, softmax: bool, renormalize: bool,
+              choice: torch.Tensor, weight: torch.Tensor) -> None:
+    _need(logits, "router logits", torch.float32); _need(choice, "moe choice", torch.int32); _need(weight, "moe weight", torch.float32)
+    T = logits.shape[0]
+    if choice.numel() != T * top or weight.numel() != T * top or logits.shape[1] < experts:
+        raise KernelError("moe_route: shapes do not agree")
+    _call("moe", "ilb_moe_route", _ptr(logits), _i(logits.stride(0)), _i(T), _i(experts), _i(top), _i(1 if softmax else 0),
+          _i(1 if renormalize else 0), _ptr(choice), _ptr(weight), _stream(logits))
+
+
+def moe_plan(choice: torch.Tensor, experts: int, block_rows: int, pos: torch.Tensor, row_pair: torch.Tensor,
+             block_expert: torch.Tensor) -> None:
+    for t, w in ((choice, "choice"), (pos, "pos"), (row_pair, "row_pair"), (block_expert, "block_expert")):
+        _need(t, "moe " + w, torch.int32)
+    rows = row_pair.numel()
+    if pos.numel() != choice.numel() or block_expert.numel() * block_rows != rows:
+        raise KernelError("moe_plan: shapes do not agree")
+    _call("moe", "ilb_moe_plan", _ptr(choice), _i(choice.numel()), _i(experts), _i(block_rows), _i(rows), _ptr(pos), _ptr(row_pair),
+          _ptr(block_expert), _stream(choice))
+
+
+def moe_gather(x: torch.Tensor, weight: Optional[torch.Tensor], row_pair: torch.Tensor, top: int, out: torch.Tensor) -> None:
+    _need(x, "moe x"); _need(out, "moe rows", x.dtype); _need(weight, "moe weight", torch.float32); _need(row_pair, "moe row_pair", torch.int32)
+    if out.shape[0] != row_pair.numel() or out.shape[1] != x.shape[1]:
+        raise KernelError("moe_gather: shapes do not agree")
+    _call("moe", "ilb_moe_gather", _ptr(x), _i(_code(x)), _ptr(weight), _ptr(row_pair), _i(out.shape[0]), _i(top), _i(x.shape[1]),
+          _ptr(out), _stream(x))
+
+
+def moe_combine(routed: torch.Tensor, pos: torch.Tensor, weight: Optional[torch.Tensor], top: int,
+                shared: Optional[torch.Tensor], gate_logit: Optional[torch.Tensor], y: torch.Tensor) -> None:
+    """y[t] += sum_j (weight[t, j] *) routed[pos[t, j]] (+ sigmoid(gate_logit[t]) * shared[t]); `gate_logit`
+    is a [T] column (any row stride) of a 32-bit matrix."""
+    _need(routed, "moe routed", torch.float32); _need(pos, "moe pos", torch.int32); _need(weight, "moe weight", torch.float32)
+    _need(shared, "moe shared", torch.float32); _need(y, "moe y", torch.float32)
+    T, H = y.shape
+    if routed.shape[1] != H or pos.numel() != T * top or (shared is not None and tuple(shared.shape) != (T, H)):
+        raise KernelError("moe_combine: shapes do not agree")
+    gate_ld = 0
+    if gate_logit is not None:
+        _need(gate_logit, "moe gate", torch.float32, contiguous=False)
+        if gate_logit.dim() != 1 or gate_logit.numel() != T:
+            raise KernelError("moe_combine: the gate must be one logit per token")
+        gate_ld = gate_logit.stride(0)
+    _call("moe", "ilb_moe_combine", _ptr(routed), _ptr(pos), _ptr(weight), _i(top), _ptr(shared), _ptr(gate_logit), _i(gate_ld),
+          _i(T), _i(H), _ptr(y), _stream(y))
+
+
+GROUP_ROWS_SIMT = 16       # rows of a block of the grouped exact product (ilb_gemm_simt_group_rows)
+
+
+def gemm_simt_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, block_group: torch.Tensor) -> None:
+    """out[rows of block b] = a[rows of block b] @ w[block_group[b]].T for blocks of 16 rows; w is
+    [groups, N, K]; blocks whose group is negative are left alone."""
+    _need(a, "gemm a"); _need(w, "gemm w", a.dtype); _need(out, "gemm out"); _need(block_group, "gemm groups", torch.int32)
+    M, K = a.shape
+    if w.dim() != 3 or w.shape[2] != K or tuple(out.shape) != (M, w.shape[1]) or block_group.numel() * GROUP_ROWS_SIMT != M:
+        raise KernelError(f"gemm_simt_grouped: shapes do not agree: a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    N = w.shape[1]
+    _call("gemm_simt", "ilb_gemm_simt_grouped", _ptr(a), _ptr(w), _ptr(out), _i(_code(a)), _i(_code(out)), _i(M), _i(N), _i(K),
+          _i(K), _i(K), _i(N), _ptr(block_group), ctypes.c_longlong(N * K), _stream(out))
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> None:
@@ -183,49 +293,66 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
 
 
 # --------------------------------------------------------------------------- attention
+ROPE_INTERLEAVED, NORM_AFTER_ROTATION, NORM_UNWEIGHTED = 1, 2, 4      # bits of `mode` (qk_norm_rope.cu)
+
+
 def qk_norm_rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optional[torch.Tensor],
                        k_weight: Optional[torch.Tensor], eps: float,
                        rope: Optional[torch.Tensor], rotary_dim: int, positions: torch.Tensor,
                        seq_of_token: torch.Tensor, block_table: Optional[torch.Tensor],
                        page_size: int, k_cache: Optional[torch.Tensor],
-                       v_cache: Optional[torch.Tensor], nq: int, nkv: int, d: int) -> None:
-    """Per-head q/k RMSNorm, rotation, q -> q_out, k/v -> cache pages (see qk_norm_rope.cu)."""
+                       v_cache: Optional[torch.Tensor], nq: int, nkv: int, d: int, dv: Optional[int] = None,
+                       mode: int = 0, v_first: Optional[torch.Tensor] = None, v_lambda: Optional[torch.Tensor] = None,
+                       v_keep: bool = False) -> None:
+    """Per-head q/k RMSNorm, rotation, q -> q_out, k/v -> cache pages (see qk_norm_rope.cu).
+    `dv`: head size of the values (default d).  `mode`: ROPE_INTERLEAVED | NORM_AFTER_ROTATION |
+    NORM_UNWEIGHTED.  `v_first` [T, nkv * dv]: with `v_keep` it receives this layer's values;
+    with `v_lambda` (a device scalar) the values become (1 - lambda) v + lambda v_first first."""
+    dv = d if dv is None else int(dv)
     _need(qkv, "qkv"); _need(q_out, "q_out", qkv.dtype)
     _need(q_weight, "q_norm weight", torch.float32); _need(k_weight, "k_norm weight", torch.float32)
     _need(rope, "rope table", torch.float32); _need(positions, "positions", torch.int32)
     _need(seq_of_token, "seq_of_token", torch.int32); _need(block_table, "block table", torch.int32)
     _need(k_cache, "k cache"); _need(v_cache, "v cache")
+    _need(v_first, "first values", qkv.dtype); _need(v_lambda, "value mixing coefficient", torch.float32)
     T = qkv.shape[0]
     if k_cache is not None:
-        if tuple(k_cache.shape[1:]) != (nkv, page_size, d) or v_cache.shape != k_cache.shape:
-            raise KernelError(f"cache shape {tuple(k_cache.shape)} is not [pages, {nkv}, {page_size}, {d}]")
+        if tuple(k_cache.shape[1:]) != (nkv, page_size, d) or tuple(v_cache.shape) != (k_cache.shape[0], nkv, page_size, dv):
+            raise KernelError(f"cache shapes {tuple(k_cache.shape)} / {tuple(v_cache.shape)} are not [pages, {nkv}, {page_size}, {d} / {dv}]")
         if block_table is None:
             raise KernelError("a cache write needs a block table")
+    v_mode = 0
+    if v_keep or v_lambda is not None:
+        if v_first is None or tuple(v_first.shape) != (T, nkv * dv) or (v_keep and v_lambda is not None):
+            raise KernelError("value mixing needs first values [tokens, nkv * dv], and either keeps or mixes them")
+        v_mode = 1 if v_keep else 2
     max_blocks = 0 if block_table is None else block_table.shape[1]
     num_pages = 0 if k_cache is None else k_cache.shape[0]
     cache_code = _code(k_cache) if k_cache is not None else _code(qkv)
     _call("qk_norm_rope", "ilb_qk_norm_rope_cache", _ptr(qkv), _ptr(q_out), _i(_code(qkv)),
           _ptr(q_weight), _ptr(k_weight), _f(eps), _ptr(rope), _i(rotary_dim), _ptr(positions),
           _ptr(seq_of_token), _ptr(block_table), _i(max_blocks), _i(page_size), _i(num_pages),
-          _ptr(k_cache), _ptr(v_cache), _i(cache_code), _i(T), _i(nq), _i(nkv), _i(d),
-          _i(qkv.shape[1]), _i(q_out.shape[1]), _stream(qkv))
+          _ptr(k_cache), _ptr(v_cache), _i(cache_code), _i(T), _i(nq), _i(nkv), _i(d), _i(dv),
+          _i(qkv.shape[1]), _i(q_out.shape[1]), _i(mode), _i(v_mode), _ptr(v_lambda), _ptr(v_first if v_mode else None),
+          _stream(qkv))
 
 
 def paged_attention_simple(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
                            v_cache: torch.Tensor, positions: torch.Tensor,
                            seq_of_token: torch.Tensor, block_table: torch.Tensor, window: int,
-                           scale: float, nq: int, nkv: int, d: int) -> None:
+                           scale: float, nq: int, nkv: int, d: int, dv: Optional[int] = None) -> None:
+    dv = d if dv is None else int(dv)
     _need(q, "attention q"); _need(out, "attention out", q.dtype)
     _need(k_cache, "k cache"); _need(v_cache, "v cache", k_cache.dtype)
     _need(positions, "positions", torch.int32); _need(seq_of_token, "seq_of_token", torch.int32)
     _need(block_table, "block table", torch.int32)
     num_pages, nkv_c, page_size, d_c = k_cache.shape
-    if (nkv_c, d_c) != (nkv, d):
+    if (nkv_c, d_c) != (nkv, d) or tuple(v_cache.shape) != (num_pages, nkv, page_size, dv):
         raise KernelError("attention: cache shape does not match the heads")
     _call("attention_simple", "ilb_paged_attention_simple", _ptr(q), _ptr(out), _i(_code(q)),
           _ptr(k_cache), _ptr(v_cache), _i(_code(k_cache)), _ptr(positions), _ptr(seq_of_token),
           _ptr(block_table), _i(block_table.shape[1]), _i(page_size), _i(num_pages),
-          _i(window or 0), _f(scale), _i(q.shape[0]), _i(nq), _i(nkv), _i(d), _i(q.shape[1]),
+          _i(window or 0), _f(scale), _i(q.shape[0]), _i(nq), _i(nkv), _i(d), _i(dv), _i(q.shape[1]),
           _i(out.shape[1]), _stream(q))
 
 
@@ -538,15 +665,16 @@ def attention_decode_fused(qkv, out, q_weight, k_weight, eps, rope_table, k_cach
 
 def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
               step, block_table: torch.Tensor, window: int, scale: float, nq: int, nkv: int,
-              d: int, workspace=None, decode_chunk: int = DECODE_CHUNK_MIN) -> None:
+              d: int, workspace=None, decode_chunk: int = DECODE_CHUNK_MIN, dv: Optional[int] = None) -> None:
     """Causal attention of the step's tokens over the cache; picks the kernel: the
     tensor-core kernels for a bfloat16 cache and a head size they are built for (split-KV
     when every sequence brings one token), else the exact kernel."""
-    fast = (q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and attention_flash_supported(d)
+    dv = d if dv is None else int(dv)
+    fast = (q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and attention_flash_supported(d) and dv == d
             and workspace is not None and FLASH_ENABLED)
-    if not fast:
+    if not fast:          # the 32-bit path, and values of another head size than the keys'
         paged_attention_simple(q, out, k_cache, v_cache, step.positions, step.seq_of_token,
-                               block_table, window, scale, nq, nkv, d)
+                               block_table, window, scale, nq, nkv, d, dv)
         return
     G = nq // nkv
     if step.decode_only and DECODE_CLUSTER_ENABLED and attention_decode_tma_supported(nq, nkv, d, k_cache.shape[2]):

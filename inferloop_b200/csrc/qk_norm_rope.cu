@@ -20,6 +20,15 @@ using namespace ilb;
 
 constexpr int kWarpsPerBlock = 4;
 
+// What a launch may ask for beside the stock order (norm with a weight, then the half-split
+// rotation): flag bits of `mode`.
+constexpr int kPairsInterleaved = 1;   // rotation pairs are (2i, 2i + 1) instead of (i, i + rd/2)
+constexpr int kNormAfterRotation = 2;  // the per-head norm follows the rotation instead of preceding it
+constexpr int kNormUnweighted = 4;     // q and k heads are divided by their root mean square, no weight
+// Value mixing across layers (`v_mode`): 1 = this layer's values are also kept in `v_first`
+// [T, nkv * dv]; 2 = v <- (1 - lambda) v + lambda v_first (lambda a device scalar) before the
+// cache write.
+
 template <typename TQ, typename TC>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 qk_norm_rope_kernel(const TQ* __restrict__ qkv, TQ* __restrict__ q_out,
@@ -28,7 +37,8 @@ qk_norm_rope_kernel(const TQ* __restrict__ qkv, TQ* __restrict__ q_out,
                     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                     const int* __restrict__ block_table, int max_blocks, int page_size,
                     int num_pages, TC* __restrict__ k_cache, TC* __restrict__ v_cache,
-                    int n_tokens, int nq, int nkv, int d, int qkv_stride, int q_out_stride) {
+                    int n_tokens, int nq, int nkv, int d, int dv, int qkv_stride, int q_out_stride,
+                    int mode, int v_mode, const float* __restrict__ v_lambda, TQ* __restrict__ v_first) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
   extern __shared__ float smem[];
@@ -37,40 +47,55 @@ qk_norm_rope_kernel(const TQ* __restrict__ qkv, TQ* __restrict__ q_out,
   const int head = blockIdx.y * kWarpsPerBlock + warp;
   const int total_heads = nq + 2 * nkv;
   if (head >= total_heads) return;
-  float* vec = smem + warp * d;
-  const TQ* src = qkv + (size_t)t * qkv_stride + (size_t)head * d;
+  const int dmax = d > dv ? d : dv;
+  float* vec = smem + warp * dmax;
   const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
+  const int width = (is_q || is_k) ? d : dv;
+  const size_t offset = (is_q || is_k) ? (size_t)head * d : (size_t)(nq + nkv) * d + (size_t)(head - nq - nkv) * dv;
+  const TQ* src = qkv + (size_t)t * qkv_stride + offset;
 
-  float ss = 0.f;
-  for (int i = lane; i < d; i += 32) {
-    const float v = to_float(src[i]);
-    vec[i] = v;
-    ss = fmaf(v, v, ss);
-  }
-  const float* weight = is_q ? q_weight : (is_k ? k_weight : nullptr);
-  if (weight != nullptr) {
-    ss = warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
-    __syncwarp();
-    for (int i = lane; i < d; i += 32) vec[i] = vec[i] * inv * weight[i];
-  }
+  for (int i = lane; i < width; i += 32) vec[i] = to_float(src[i]);
   __syncwarp();
+  const float* weight = is_q ? q_weight : (is_k ? k_weight : nullptr);
+  const bool normed = (is_q || is_k) && (weight != nullptr || (mode & kNormUnweighted));
+  auto norm = [&]() {
+    float ss = 0.f;
+    for (int i = lane; i < width; i += 32) ss = fmaf(vec[i], vec[i], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int i = lane; i < width; i += 32) vec[i] = weight != nullptr ? vec[i] * inv * weight[i] : vec[i] * inv;
+    __syncwarp();
+  };
+  if (normed && !(mode & kNormAfterRotation)) norm();
   if ((is_q || is_k) && rope_table != nullptr) {
     const int half = rotary_dim / 2;
     const float2* cs = rope_table + (size_t)t * half;
+    const bool inter = mode & kPairsInterleaved;
     for (int i = lane; i < half; i += 32) {
-      const float a = vec[i], b = vec[i + half];
+      const int ia = inter ? 2 * i : i, ib = inter ? 2 * i + 1 : i + half;
+      const float a = vec[ia], b = vec[ib];
       const float2 c = cs[i];
       // Products and sums rounded separately, as the reference's scalar code does.
-      vec[i] = __fsub_rn(__fmul_rn(a, c.x), __fmul_rn(b, c.y));
-      vec[i + half] = __fadd_rn(__fmul_rn(a, c.y), __fmul_rn(b, c.x));
+      vec[ia] = __fsub_rn(__fmul_rn(a, c.x), __fmul_rn(b, c.y));
+      vec[ib] = __fadd_rn(__fmul_rn(a, c.y), __fmul_rn(b, c.x));
     }
     __syncwarp();
   }
+  if (normed && (mode & kNormAfterRotation)) norm();
   if (is_q) {
     TQ* dst = q_out + (size_t)t * q_out_stride + (size_t)head * d;
     for (int i = lane; i < d; i += 32) dst[i] = from_float<TQ>(vec[i]);
     return;
+  }
+  const int kvh = is_k ? head - nq : head - nq - nkv;
+  if (!is_k && v_mode != 0) {
+    TQ* keep = v_first + ((size_t)t * nkv + kvh) * dv;
+    if (v_mode == 1) {
+      for (int i = lane; i < dv; i += 32) keep[i] = from_float<TQ>(vec[i]);
+    } else {
+      const float lam = *v_lambda;
+      for (int i = lane; i < dv; i += 32) vec[i] = fmaf(lam, to_float(keep[i]), (1.0f - lam) * vec[i]);
+    }
   }
   if (k_cache == nullptr) return;
   const int pos = positions[t];
@@ -79,10 +104,9 @@ qk_norm_rope_kernel(const TQ* __restrict__ qkv, TQ* __restrict__ q_out,
   if (blk < 0 || blk >= max_blocks) return;
   const int page = block_table[(size_t)seq * max_blocks + blk];
   if (page < 0 || page >= num_pages) return;   // never write outside the pool
-  const int kvh = is_k ? head - nq : head - nq - nkv;
   TC* dst = (is_k ? k_cache : v_cache) +
-            (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * d;
-  for (int i = lane; i < d; i += 32) dst[i] = from_float<TC>(vec[i]);
+            (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * width;
+  for (int i = lane; i < width; i += 32) dst[i] = from_float<TC>(vec[i]);
 }
 
 // The common geometry, bfloat16 throughout, head size 128, rotation over the whole head: one
@@ -221,28 +245,35 @@ qk_norm_rope_d128_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* _
 }
 
 // dtype: element type of qkv and q_out; cache_dtype: element type of the cache.
-// q_weight / k_weight may be null (no per-head norm); rope_table may be null (no
-// rotation); k_cache / v_cache may be null (this layer does not write a cache).
+// q_weight / k_weight may be null (no weighted per-head norm); rope_table may be null (no
+// rotation); k_cache / v_cache may be null (this layer does not write a cache).  Keys have
+// head size d, values dv (the V cache is [pages, nkv, page_size, dv]); `mode` and `v_mode`
+// are described above the kernel.
 ILB_EXPORT int ilb_qk_norm_rope_cache(
     const void* qkv, void* q_out, int dtype, const float* q_weight, const float* k_weight,
     float eps, const float* rope_table, int rotary_dim, const int* positions,
     const int* seq_of_token, const int* block_table, int max_blocks, int page_size,
     int num_pages, void* k_cache, void* v_cache, int cache_dtype, int n_tokens, int nq, int nkv,
-    int d, int qkv_stride, int q_out_stride, cudaStream_t stream) {
-  ILB_REQUIRE(n_tokens >= 0 && nq > 0 && nkv > 0 && d > 0, "qk_norm_rope: bad sizes");
-  ILB_REQUIRE(d <= 1024, "qk_norm_rope: head size %d exceeds 1024", d);
+    int d, int dv, int qkv_stride, int q_out_stride, int mode, int v_mode, const float* v_lambda, void* v_first,
+    cudaStream_t stream) {
+  ILB_REQUIRE(n_tokens >= 0 && nq > 0 && nkv > 0 && d > 0 && dv > 0, "qk_norm_rope: bad sizes");
+  ILB_REQUIRE(d <= 1024 && dv <= 1024, "qk_norm_rope: head size %d / %d exceeds 1024", d, dv);
   ILB_REQUIRE(rope_table == nullptr || (rotary_dim > 0 && rotary_dim % 2 == 0 && rotary_dim <= d),
               "qk_norm_rope: rotary dimension %d must be even and at most the head size %d",
               rotary_dim, d);
-  ILB_REQUIRE(qkv_stride >= (nq + 2 * nkv) * d && q_out_stride >= nq * d,
+  ILB_REQUIRE(qkv_stride >= (nq + nkv) * d + nkv * dv && q_out_stride >= nq * d,
               "qk_norm_rope: strides too small");
   ILB_REQUIRE((k_cache == nullptr) == (v_cache == nullptr), "qk_norm_rope: need both caches or none");
   ILB_REQUIRE(k_cache == nullptr || (page_size > 0 && max_blocks > 0 && num_pages > 0),
               "qk_norm_rope: bad cache geometry");
   ILB_REQUIRE(dtype == cache_dtype || k_cache == nullptr || (dtype == kF32 && cache_dtype == kBF16) ||
               (dtype == kBF16 && cache_dtype == kF32), "qk_norm_rope: unknown dtypes");
+  ILB_REQUIRE(mode >= 0 && mode < 8 && v_mode >= 0 && v_mode <= 2, "qk_norm_rope: unknown mode %d / %d", mode, v_mode);
+  ILB_REQUIRE(v_mode == 0 || v_first != nullptr, "qk_norm_rope: value mixing needs the buffer of the first values");
+  ILB_REQUIRE(v_mode != 2 || v_lambda != nullptr, "qk_norm_rope: value mixing needs its coefficient");
   if (n_tokens == 0) return 0;
-  if (dtype == kBF16 && (cache_dtype == kBF16 || k_cache == nullptr) && d == 128 && (rope_table == nullptr || rotary_dim == d) &&
+  if (dtype == kBF16 && (cache_dtype == kBF16 || k_cache == nullptr) && d == 128 && dv == 128 && mode == 0 && v_mode == 0 &&
+      (rope_table == nullptr || rotary_dim == d) &&
       qkv_stride % 8 == 0 && q_out_stride % 8 == 0 && ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
       ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0) && ((uintptr_t)rope_table % 16 == 0) &&
       ((uintptr_t)q_weight % 16 == 0) && ((uintptr_t)k_weight % 16 == 0)) {
@@ -259,12 +290,13 @@ ILB_EXPORT int ilb_qk_norm_rope_cache(
     return check_launch("qk_norm_rope_cache");
   }
   dim3 grid(n_tokens, (nq + 2 * nkv + kWarpsPerBlock - 1) / kWarpsPerBlock);
-  const size_t smem = (size_t)kWarpsPerBlock * d * sizeof(float);
+  const size_t smem = (size_t)kWarpsPerBlock * (d > dv ? d : dv) * sizeof(float);
 #define ILB_LAUNCH(TQ, TC)                                                                   \
   ilb::launch(qk_norm_rope_kernel<TQ, TC>, dim3(grid), dim3(kWarpsPerBlock * 32), smem, stream,                    \
       (const TQ*)qkv, (TQ*)q_out, q_weight, k_weight, eps, (const float2*)rope_table,         \
       rotary_dim, positions, seq_of_token, block_table, max_blocks, page_size, num_pages,     \
-      (TC*)k_cache, (TC*)v_cache, n_tokens, nq, nkv, d, qkv_stride, q_out_stride)
+      (TC*)k_cache, (TC*)v_cache, n_tokens, nq, nkv, d, dv, qkv_stride, q_out_stride, mode, v_mode,     \
+      v_lambda, (TQ*)v_first)
   if (dtype == kF32 && cache_dtype == kF32) ILB_LAUNCH(float, float);
   else if (dtype == kBF16 && cache_dtype == kBF16) ILB_LAUNCH(__nv_bfloat16, __nv_bfloat16);
   else if (dtype == kF32 && cache_dtype == kBF16) ILB_LAUNCH(float, __nv_bfloat16);

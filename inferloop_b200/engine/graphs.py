@@ -252,7 +252,7 @@ class DecodeGraphs:
         recorded segments read)."""
         r = self.runner
         ctx = self._prepare(entries, bucket, rec.ints)
-        hidden = r.ctx.workspace.buffer("model.hidden", (ctx.n_tokens, r.spec.hidden_size), torch.float32)
+        hidden = r.model.hidden_buffer(ctx.n_tokens)
         for seg in rec.segments:
             if seg[0] == "graph":
                 seg[1].replay()

@@ -32,6 +32,7 @@ def build_parser() -> argparse.ArgumentParser:
                    help="most tokens live requests hold at any time (each rounded up to 64)")
     p.add_argument("--device", default="cuda:0")
     p.add_argument("--block-size", type=int, default=PAGE_TOKENS, help="tokens per cache page")
+    p.add_argument("--max-requests", type=int, default=4, help="requests that may be live at a time (state slots)")
     return p
 
 
@@ -52,7 +53,7 @@ def main(argv: List[str] | None = None) -> int:
     num_pages = -(-args.max_tokens // args.block_size)
     runner = ModelRunner.from_folder(
         args.model, dtype=args.dtype, device=args.device, page_size=args.block_size,
-        num_pages=num_pages, max_requests=16,
+        num_pages=num_pages, max_requests=max(1, args.max_requests),
         progress=lambda m: print(f"[trace_run] {m}", file=sys.stderr, flush=True))
     for line_no, line in enumerate(sys.stdin, 1):
         line = line.strip()

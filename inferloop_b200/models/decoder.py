@@ -80,7 +80,7 @@ class DecoderModel:
         s = self.spec
         size = torch.empty((), dtype=self.ctx.dtype).element_size()
         blocks = max((b.scratch_bytes(tokens) for b in self.blocks), default=0)
-        return (tokens * s.hidden_size * 4 + blocks + logit_rows * s.hidden_size * (4 + size)
+        return (tokens * s.hidden_size * s.residual_streams * 4 + blocks + logit_rows * s.hidden_size * (4 + size)
                 + logit_rows * s.vocab_size * 4)
 
     # ------------------------------------------------------------------ run
@@ -92,13 +92,17 @@ class DecoderModel:
         return self.forward_head(hidden, step)
 
     # The three pieces of `forward`, for a caller that runs (or records) a step in segments.
+    def hidden_buffer(self, tokens: int) -> torch.Tensor:
+        """The 32-bit residual stream of a step: [tokens, residual_streams * hidden_size]."""
+        s = self.spec
+        return self.ctx.workspace.buffer("model.hidden", (tokens, s.residual_streams * s.hidden_size), torch.float32)
+
     def forward_embed(self, step) -> torch.Tensor:
-        s, ws = self.spec, self.ctx.workspace
-        hidden = ws.buffer("model.hidden", (step.n_tokens, s.hidden_size), torch.float32)
+        s = self.spec
+        hidden = self.hidden_buffer(step.n_tokens)
         ops.scope("embedding")
-        ops.embed(step.tokens, self.embedding, hidden)
-        if s.embedding_scale is not None and s.embedding_scale != 1.0:
-            ops.scale_cap_inplace(hidden, float(s.embedding_scale), 0.0)
+        ops.embed(step.tokens, self.embedding, hidden, 1.0 if s.embedding_scale is None else float(s.embedding_scale),
+                  s.residual_streams)
         return hidden
 
     def forward_entries(self, hidden: torch.Tensor, step, caches, first: int, last: int) -> None:
@@ -113,7 +117,7 @@ class DecoderModel:
         if R == 0:
             return ws.buffer("model.logits", (0, s.vocab_size), torch.float32)
         rows = ws.buffer("model.rows", (R, s.hidden_size), torch.float32)
-        ops.gather_rows(hidden, step.logit_rows, rows)
+        ops.gather_rows(hidden, step.logit_rows, rows, s.residual_streams)      # (the sum of the streams)
         normed = ws.buffer("model.rows_normed", (R, s.hidden_size), self.ctx.dtype)
         self.final_norm.forward(rows, normed)
         logits = ws.buffer("model.logits", (R, s.vocab_size), torch.float32)

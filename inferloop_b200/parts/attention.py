@@ -10,8 +10,17 @@ h / (nq / nkv) and scale 1/sqrt(head_dim)
 residual (:358-363).  Biases, where the spec asks for them, are added in 32-bit right
 after each projection.
 
-The three projection matrices are concatenated at load into one [(nq + 2 nkv) d, H]
+The three projection matrices are concatenated at load into one [(nq + nkv) d + nkv dv, H]
 matrix so one GEMM produces q|k|v.
+
+What a description may vary beyond that (all spec parameters, the defaults give the layer
+above): `v_head_dim` (values of another head size than queries and keys), `bias` = True /
+False / "qkv" (no bias on the output projection), `qk_norm` = True (weight [head_dim]) or
+"unweighted" (q and k divided by their root mean square), `qk_norm_after_rotation`,
+`scale` (the multiplier of q.k), a position kind whose pairs are interleaved, tensor names
+(`names`: pairs (role, name under the prefix)), and `value_mix` = "first" | "mixed": the first
+such layer of a model keeps its values of the step's tokens, every later one caches
+(1 - lambda) v + lambda v_first with its own learned scalar lambda.
 """
 from __future__ import annotations
 
@@ -41,36 +50,61 @@ class GQAttention(Mixer):
         self.d = int(spec["head_dim"])
         if self.nq % self.nkv:
             raise ValueError(f"{self.nq} query heads are not a multiple of {self.nkv} kv heads")
-        self.qk_norm = bool(spec.get("qk_norm", False))
+        self.dv = int(spec.get("v_head_dim") or self.d)
+        qk_norm = spec.get("qk_norm", False)
+        if qk_norm not in (False, True, "unweighted"):
+            raise ValueError(f"qk_norm must be False, True or 'unweighted', found {qk_norm!r}")
+        self.qk_norm = qk_norm is True                       # with a weight per head element
+        self.qk_norm_unweighted = qk_norm == "unweighted"
+        self.qk_norm_after = bool(spec.get("qk_norm_after_rotation", False))
         self.qk_norm_eps = float(spec.get("qk_norm_eps", 1e-6))
-        self.bias = bool(spec.get("bias", False))
+        bias = spec.get("bias", False)
+        if bias not in (False, True, "qkv"):
+            raise ValueError(f"bias must be False, True or 'qkv', found {bias!r}")
+        self.bias = bool(bias)                               # q, k, v
+        self.out_bias = bias is True
         self.window = spec.get("window")
-        self.scale = 1.0 / math.sqrt(self.d)
+        self.scale = float(spec["scale"]) if spec.get("scale") is not None else 1.0 / math.sqrt(self.d)
+        self.value_mix = spec.get("value_mix")
+        if self.value_mix not in (None, "first", "mixed"):
+            raise ValueError(f"value_mix must be None, 'first' or 'mixed', found {self.value_mix!r}")
         # split-KV decode cuts the keys at multiples of this, fixed per model so that the
         # cut never depends on the batch
         self.decode_chunk = ops.decode_chunk_for(int(spec.get("max_positions", 4096)))
         self.position = registry.build("position", spec["position"], ctx)
         self.rotary_dim = int(spec["position"].get("rotary_dim", 0))
         p = prefix
-        self.names = {k: p + v for k, v in {
-            "q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
-            "qb": "q_proj.bias", "kb": "k_proj.bias", "vb": "v_proj.bias", "ob": "o_proj.bias",
-            "qn": "q_norm.weight", "kn": "k_norm.weight"}.items()}
-        self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.q_norm = self.k_norm = None
+        names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+                 "qb": "q_proj.bias", "kb": "k_proj.bias", "vb": "v_proj.bias", "ob": "o_proj.bias",
+                 "qn": "q_norm.weight", "kn": "k_norm.weight", "vmix": "v_mix"}
+        for role, name in spec.get("names", ()):
+            if role not in names:
+                raise ValueError(f"attention has no tensor role {role!r}")
+            names[role] = name
+        self.names = {k: p + v for k, v in names.items()}
+        self.mode = ((ops.ROPE_INTERLEAVED if getattr(self.position, "interleaved", False) else 0)
+                     | (ops.NORM_AFTER_ROTATION if self.qk_norm_after else 0)
+                     | (ops.NORM_UNWEIGHTED if self.qk_norm_unweighted else 0))
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.q_norm = self.k_norm = self.v_lambda = None
 
     # ------------------------------------------------------------------ weights
     def declare_weights(self) -> List[WeightDecl]:
-        n, d, H = self.names, self.d, self.hidden
+        n, d, dv, H = self.names, self.d, self.dv, self.hidden
         out = [WeightDecl(n["q"], (self.nq * d, H)), WeightDecl(n["k"], (self.nkv * d, H)),
-               WeightDecl(n["v"], (self.nkv * d, H)), WeightDecl(n["o"], (H, self.nq * d))]
+               WeightDecl(n["v"], (self.nkv * dv, H)), WeightDecl(n["o"], (H, self.nq * dv))]
         if self.bias:
             out += [WeightDecl(n["qb"], (self.nq * d,), "vector", "bias"),
                     WeightDecl(n["kb"], (self.nkv * d,), "vector", "bias"),
-                    WeightDecl(n["vb"], (self.nkv * d,), "vector", "bias"),
-                    WeightDecl(n["ob"], (H,), "vector", "bias")]
+                    WeightDecl(n["vb"], (self.nkv * dv,), "vector", "bias")]
+        if self.out_bias:
+            out.append(WeightDecl(n["ob"], (H,), "vector", "bias"))
         if self.qk_norm:
             out += [WeightDecl(n["qn"], (d,), "vector", "norm"),
                     WeightDecl(n["kn"], (d,), "vector", "norm")]
+        if self.value_mix == "mixed":
+            out.append(WeightDecl(n["vmix"], (), "vector", "mix"))
+        elif bool(self.spec.get("value_mix_tensor_unused", False)):
+            out.append(WeightDecl(n["vmix"], (), "vector", "mix", optional=True))    # stored, never read
         return out
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
@@ -79,31 +113,40 @@ class GQAttention(Mixer):
         self.w_o = tensors[n["o"]].contiguous()
         if self.bias:
             self.b_qkv = torch.cat([tensors[n["qb"]], tensors[n["kb"]], tensors[n["vb"]]]).contiguous()
+        if self.out_bias:
             self.b_o = tensors[n["ob"]].contiguous()
+        if self.value_mix == "mixed":
+            self.v_lambda = tensors[n["vmix"]].reshape(1).contiguous()
         if self.qk_norm:
             self.q_norm = tensors[n["qn"]].contiguous()
             self.k_norm = tensors[n["kn"]].contiguous()
 
     def cache_needs(self) -> CacheNeeds:
-        return CacheNeeds(paged=PagedKVNeed(self.nkv, self.d, self.window))
+        return CacheNeeds(paged=PagedKVNeed(self.nkv, self.d, self.window, self.dv if self.dv != self.d else None))
 
     def scratch_bytes(self, tokens: int) -> int:
         size = torch.empty((), dtype=self.ctx.dtype).element_size()
-        width = (self.nq + 2 * self.nkv) * self.d
-        return tokens * ((width + 2 * self.nq * self.d) * size + self.rotary_dim * 4)
+        width = (self.nq + self.nkv) * self.d + self.nkv * self.dv
+        kept = self.nkv * self.dv if self.value_mix else 0
+        return tokens * ((width + self.nq * (self.d + self.dv) + kept) * size + self.rotary_dim * 4)
 
     # ------------------------------------------------------------------ run
     def forward(self, x: torch.Tensor, residual: torch.Tensor, step, cache) -> None:
         T = x.shape[0]
         ws, dt = self.ctx.workspace, self.ctx.dtype
-        width = (self.nq + 2 * self.nkv) * self.d
+        width = (self.nq + self.nkv) * self.d + self.nkv * self.dv
         qkv = ws.buffer("attn.qkv", (T, width), dt)
         ops.scope("attention.qkv_projection")
         linear(x, self.w_qkv, qkv, self.b_qkv)
         table = step.block_tables[cache.group]
         ops.scope("attention.position_table")
         rope = self.position.table(step)
-        if (step.decode_only and cache.k is not None and ops.attention_decode_fused_supported(
+        v_first = None
+        if self.value_mix is not None:
+            # the step's tokens' values of the first layer that mixes: kept by it, read by the later ones
+            v_first = ws.buffer(f"attn.v_first/{self.nkv}x{self.dv}", (T, self.nkv * self.dv), dt)
+        stock = self.mode == 0 and self.dv == self.d and self.value_mix is None
+        if (stock and step.decode_only and cache.k is not None and ops.attention_decode_fused_supported(
                 dt, cache.k.dtype, self.nq, self.nkv, self.d, cache.page_size, self.rotary_dim, rope is not None)):
             # one token per sequence: norm, rotation and the cache write of the new key and
             # value happen inside the attention kernel
@@ -122,11 +165,12 @@ class GQAttention(Mixer):
             qkv, q, self.q_norm, self.k_norm, self.qk_norm_eps, rope,
             self.rotary_dim, step.positions, step.seq_of_token, table, cache.page_size,
             cache.k if cache.writable else None, cache.v if cache.writable else None,
-            self.nq, self.nkv, self.d)
-        o = ws.buffer("attn.o", (T, self.nq * self.d), dt)
+            self.nq, self.nkv, self.d, self.dv, self.mode, v_first=v_first,
+            v_lambda=self.v_lambda if self.value_mix == "mixed" else None, v_keep=self.value_mix == "first")
+        o = ws.buffer("attn.o", (T, self.nq * self.dv), dt)
         ops.scope("attention.attention")
         ops.attention(q, o, cache.k, cache.v, step, table, self.window or 0, self.scale,
-                      self.nq, self.nkv, self.d, workspace=ws, decode_chunk=self.decode_chunk)
+                      self.nq, self.nkv, self.d, workspace=ws, decode_chunk=self.decode_chunk, dv=self.dv)
         ops.scope("attention.o_projection")
         linear(o, self.w_o, residual, self.b_o, accumulate=True)
 

@@ -88,6 +88,11 @@ class PagedKVNeed:
     kv_heads: int
     head_dim: int
     window: Optional[int] = None     # None: all keys are kept; n: only the last n are read
+    v_head_dim: Optional[int] = None  # head size of the values when it is not the keys'
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)

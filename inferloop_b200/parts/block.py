@@ -32,11 +32,14 @@ class PreNormBlock(Block):
         return all(p.graph_safe for p in (self.norm1, self.mixer, self.norm2, self.ffn))
 
     def declare_weights(self) -> List[WeightDecl]:
-        return (self.norm1.declare_weights() + self.mixer.declare_weights()
-                + self.norm2.declare_weights() + self.ffn.declare_weights())
+        second = self.norm2.declare_weights()
+        if getattr(self.ffn, "absent", False):        # the absent sublayer's norm may be stored; it is not read
+            second = [WeightDecl(d.name, d.shape, d.role, d.init, d.root, True) for d in second]
+        return self.norm1.declare_weights() + self.mixer.declare_weights() + second + self.ffn.declare_weights()
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        for part in (self.norm1, self.mixer, self.norm2, self.ffn):
+        absent = getattr(self.ffn, "absent", False)
+        for part in (self.norm1, self.mixer) + (() if absent else (self.norm2, self.ffn)):
             part.bind(tensors)
 
     def cache_needs(self) -> CacheNeeds:
@@ -53,6 +56,8 @@ class PreNormBlock(Block):
         self.norm1.forward(hidden, normed)
         ops.scope("mixer")
         self.mixer.forward(normed, hidden, step, cache)
+        if getattr(self.ffn, "absent", False):        # a layer that has only its mixer
+            return
         ops.scope("norm")
         self.norm2.forward(hidden, normed)
         ops.scope("feed_forward")

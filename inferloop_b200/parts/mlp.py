@@ -29,8 +29,12 @@ class SwiGLU(FeedForward):
         super().__init__(spec, ctx, prefix)
         self.hidden = int(spec["hidden_size"])
         self.inter = int(spec["intermediate_size"])
-        self.names = {"gate": prefix + "gate_proj.weight", "up": prefix + "up_proj.weight",
-                      "down": prefix + "down_proj.weight"}
+        names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+        for role, name in spec.get("names", ()):            # a description may name the tensors otherwise
+            if role not in names:
+                raise ValueError(f"swiglu has no tensor role {role!r}")
+            names[role] = name
+        self.names = {k: prefix + v for k, v in names.items()}
         self.w_gate_up = self.w_down = None
         self.fused = False
 
@@ -58,7 +62,8 @@ class SwiGLU(FeedForward):
         fused = self.ctx.dtype == torch.bfloat16 and self.inter % 64 == 0 and self.hidden % 8 == 0
         return tokens * self.inter * size * (1 if fused else 3)
 
-    def forward(self, x: torch.Tensor, residual: torch.Tensor, step) -> None:
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, step, accumulate: bool = True) -> None:
+        """residual += the feed-forward of x (with `accumulate` False: residual = it)."""
         T = x.shape[0]
         ws, dt = self.ctx.workspace, self.ctx.dtype
         act = ws.buffer("mlp.act", (T, self.inter), dt)
@@ -73,7 +78,17 @@ class SwiGLU(FeedForward):
             ops.scope("feed_forward.swiglu")
             ops.silu_mul(gate_up, act)
         ops.scope("feed_forward.down")
-        linear(act, self.w_down, residual, accumulate=True)
+        linear(act, self.w_down, residual, accumulate=accumulate)
+
+
+class NoFeedForward(FeedForward):
+    """A layer that has only its mixer: blocks skip the feed-forward's norm and sublayer."""
+    graph_safe = True
+    absent = True
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, step) -> None:
+        return None
 
 
 register("feed_forward", "swiglu", SwiGLU)
+register("feed_forward", "none", NoFeedForward)

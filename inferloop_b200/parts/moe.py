@@ -1,0 +1,136 @@
+"""Routed feed-forward: every token runs `top_k` of `experts` small SwiGLU feed-forwards.
+
+  z = W_router x                (32-bit; x may be the compute dtype's rounding)
+  s = sigmoid(z)  or  softmax(z) over the experts          (`score`)
+  the top_k experts with the largest s (ties to the lower index), weights w = their s,
+  divided by their sum when `renormalize`
+  y = sum_j expert_j(w_j x)     (`weight_on` = "input")   or   sum_j w_j expert_j(x)   ("output")
+  y += sigmoid(W_gate x) * shared(x)    when the description has a shared expert (`shared_inter`;
+  `shared_gate` False leaves the multiplier out)
+
+The experts' matrices are stacked at load into [experts, 2 I, H] (gate rows, then up rows) and
+[experts, H, I].  A step sorts its (token, choice) pairs by expert on the device into rows
+padded so that a block of rows belongs to one expert (csrc/moe.cu), gathers the inputs into
+that order, runs the two grouped products over it, and adds each token's rows back in choice
+order together with the shared expert.  No size depends on the routing, so decode steps can
+be replayed as recorded graphs.  The router's and the gate's logits come from one exact
+32-bit product over the rows [W_router; W_gate].
+"""
+from __future__ import annotations
+
+from typing import List, Mapping
+
+import torch
+
+from ..config.spec import PartSpec
+from ..csrc import ops
+from ..weights.decl import WeightDecl
+from .base import FeedForward
+from .mlp import SwiGLU
+from .registry import register
+
+
+class RoutedExperts(FeedForward):
+    graph_safe = True
+
+    def __init__(self, spec, ctx, prefix: str = "") -> None:
+        super().__init__(spec, ctx, prefix)
+        self.hidden = int(spec["hidden_size"])
+        self.experts = int(spec["experts"])
+        self.top = int(spec["top_k"])
+        self.inter = int(spec["expert_inter"])
+        self.score = str(spec.get("score", "softmax"))
+        self.renormalize = bool(spec.get("renormalize", False))
+        self.weight_on = str(spec.get("weight_on", "output"))
+        self.shared_inter = int(spec.get("shared_inter") or 0)
+        self.shared_gate = bool(spec.get("shared_gate", False)) and self.shared_inter > 0
+        if self.score not in ("sigmoid", "softmax"):
+            raise ValueError(f"router score must be 'sigmoid' or 'softmax', found {self.score!r}")
+        if self.weight_on not in ("input", "output"):
+            raise ValueError(f"weight_on must be 'input' or 'output', found {self.weight_on!r}")
+        if not 0 < self.top <= self.experts:
+            raise ValueError(f"top_k {self.top} of {self.experts} experts")
+        # tensor names under the prefix: {e} is the expert's number
+        names = {"router": "router.weight", "gate": "experts.{e}.gate_proj.weight", "up": "experts.{e}.up_proj.weight",
+                 "down": "experts.{e}.down_proj.weight", "shared_gate": "shared_expert_gate.weight",
+                 "shared_prefix": "shared_expert."}
+        for role, name in spec.get("names", ()):
+            if role not in names:
+                raise ValueError(f"routed feed-forward has no tensor role {role!r}")
+            names[role] = name
+        self.names = {k: prefix + v for k, v in names.items()}
+        self.shared = None
+        if self.shared_inter:
+            self.shared = SwiGLU(PartSpec.make("swiglu", hidden_size=self.hidden, intermediate_size=self.shared_inter,
+                                               names=tuple(spec.get("shared_names", ()))), ctx, self.names["shared_prefix"])
+        self.w_router = self.w_gate_up = self.w_down = None
+
+    # ------------------------------------------------------------------ weights
+    def declare_weights(self) -> List[WeightDecl]:
+        n, H, I = self.names, self.hidden, self.inter
+        out = [WeightDecl(n["router"], (self.experts, H))]
+        for e in range(self.experts):
+            out += [WeightDecl(n["gate"].format(e=e), (I, H)), WeightDecl(n["up"].format(e=e), (I, H)),
+                    WeightDecl(n["down"].format(e=e), (H, I))]
+        if self.shared is not None:
+            out += self.shared.declare_weights()
+        if self.shared_gate:
+            out.append(WeightDecl(n["shared_gate"], (1, H)))
+        return out
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        n = self.names
+        rows = [tensors[n["router"]]] + ([tensors[n["shared_gate"]]] if self.shared_gate else [])
+        self.w_router = torch.cat(rows, dim=0).contiguous()
+        self.w_gate_up = torch.stack([torch.cat([tensors[n["gate"].format(e=e)], tensors[n["up"].format(e=e)]], dim=0)
+                                      for e in range(self.experts)]).contiguous()
+        self.w_down = torch.stack([tensors[n["down"].format(e=e)] for e in range(self.experts)]).contiguous()
+        if self.shared is not None:
+            self.shared.bind(tensors)
+
+    def _rows(self, tokens: int) -> int:
+        return ops.moe_plan_rows(tokens * self.top, self.experts, ops.GROUP_ROWS_SIMT)
+
+    def scratch_bytes(self, tokens: int) -> int:
+        size = torch.empty((), dtype=self.ctx.dtype).element_size()
+        rows = self._rows(tokens)
+        own = rows * ((self.hidden + 3 * self.inter) * size + self.hidden * 4) + tokens * (self.experts + 1 + 3 * self.top) * 4 + rows * 8
+        shared = (self.shared.scratch_bytes(tokens) + tokens * self.hidden * 4) if self.shared is not None else 0
+        return own + shared
+
+    # ------------------------------------------------------------------ run
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, step) -> None:
+        T, H, I, E, K = x.shape[0], self.hidden, self.inter, self.experts, self.top
+        ws, dt = self.ctx.workspace, self.ctx.dtype
+        block = ops.GROUP_ROWS_SIMT
+        rows = self._rows(T)
+        ops.scope("feed_forward.router")
+        logits = ws.buffer("moe.logits", (T, self.w_router.shape[0]), torch.float32)
+        ops.gemm_simt(x, self.w_router, logits)
+        choice = ws.buffer("moe.choice", (T * K,), torch.int32)
+        weight = ws.buffer("moe.weight", (T * K,), torch.float32)
+        ops.moe_route(logits, E, K, self.score == "softmax", self.renormalize, choice, weight)
+        pos = ws.buffer("moe.pos", (T * K,), torch.int32)
+        row_pair = ws.buffer("moe.row_pair", (rows,), torch.int32)
+        block_expert = ws.buffer("moe.block_expert", (rows // block,), torch.int32)
+        ops.moe_plan(choice, E, block, pos, row_pair, block_expert)
+        ops.scope("feed_forward.experts")
+        a = ws.buffer("moe.rows", (rows, H), dt)
+        ops.moe_gather(x, weight if self.weight_on == "input" else None, row_pair, K, a)
+        gate_up = ws.buffer("moe.gate_up", (rows, 2 * I), dt)
+        ops.gemm_simt_grouped(a, self.w_gate_up, gate_up, block_expert)
+        act = ws.buffer("moe.act", (rows, I), dt)
+        ops.silu_mul(gate_up, act)
+        routed = ws.buffer("moe.routed", (rows, H), torch.float32)
+        ops.gemm_simt_grouped(act, self.w_down, routed, block_expert)
+        shared_out = None
+        if self.shared is not None:
+            ops.scope("feed_forward.shared_expert")
+            shared_out = ws.buffer("moe.shared", (T, H), torch.float32)
+            self.shared.forward(x, shared_out, step, accumulate=False)
+        ops.scope("feed_forward.combine")
+        ops.moe_combine(routed, pos, weight if self.weight_on == "output" else None, K, shared_out,
+                        logits[:, E] if self.shared_gate else None, residual)
+
+
+register("feed_forward", "routed_experts", RoutedExperts)

@@ -15,13 +15,14 @@ from .registry import register
 
 class RMSNorm(Norm):
     graph_safe = True
-    """spec: eps; width is given by the owner through `prefix`-named weight of `width`."""
+    """spec: eps; optional `weight_suffix` (default "weight"): the weight is the tensor
+    prefix + suffix, of the width that the owner gives."""
 
     def __init__(self, spec, ctx, prefix: str = "", width: int = 0, name: str = "weight") -> None:
         super().__init__(spec, ctx, prefix)
         self.eps = float(spec["eps"])
         self.width = int(width or spec.get("width", 0))
-        self.weight_name = prefix + name
+        self.weight_name = prefix + str(spec.get("weight_suffix", name))
         self.weight = None
 
     def declare_weights(self) -> List[WeightDecl]:

@@ -65,4 +65,4 @@ def _ensure_builtin() -> None:
     if _BUILTIN_DONE:
         return
     _BUILTIN_DONE = True
-    from . import attention, block, logits, mlp, norm, rope  # noqa: F401  (they register themselves)
+    from . import attention, block, hyper, logits, mlp, moe, norm, rope  # noqa: F401  (they register themselves)

@@ -22,6 +22,8 @@ from .registry import register
 
 class RopeNeox(PositionEncoding):
     graph_safe = True
+    interleaved = False
+
     def __init__(self, spec, ctx, prefix: str = "") -> None:
         super().__init__(spec, ctx, prefix)
         self.theta = float(spec["theta"])
@@ -32,7 +34,7 @@ class RopeNeox(PositionEncoding):
 
     @property
     def key(self):
-        return ("rope_neox", self.theta, self.rotary_dim)
+        return ("rope", self.theta, self.rotary_dim)
 
     def inv_freq(self) -> torch.Tensor:
         if self._inv_freq is None:
@@ -52,13 +54,26 @@ class RopeNeox(PositionEncoding):
         return cached
 
 
+class RopeInterleaved(RopeNeox):
+    """The same angles, but the rotation pairs are neighbours: element 2i with element 2i + 1,
+    i in [0, rd/2): (u, v) -> (u cos a - v sin a, v cos a + u sin a), a = pos * theta^(-2i/rd).
+    The table is the half-split encoding's; the mixer asks `interleaved` how to pair."""
+    interleaved = True
+
+    @property
+    def key(self):
+        return ("rope", self.theta, self.rotary_dim)
+
+
 class NoPosition(PositionEncoding):
     graph_safe = True
     """A mixer that wants no position signal."""
+    interleaved = False
 
     def table(self, step):
         return None
 
 
 register("position", "rope_neox", RopeNeox)
+register("position", "rope_interleaved", RopeInterleaved)
 register("position", "none", NoPosition)

@@ -14,9 +14,11 @@ class WeightDecl:
            keeps a 32-bit tensor as stored and widens a 16-bit one without loss;
            "int" is an integer table held as int32.
     init:  distribution used by the random-weights mode: "normal" N(0, 0.02),
-           "norm" 1 + N(0, 0.1), "bias" N(0, 0.02), "zeros".
+           "norm" 1 + N(0, 0.1), "bias" N(0, 0.02), "mix" 0.5 + N(0, 0.1), "zeros".
     root:  True when the name is not under the model's weight prefix
            (`lm_head.weight`, crates/foundation/spi/src/model.rs:220-226).
+    optional: a tensor that a file may hold although the model does not read it (or may leave
+           out): it is neither missing nor unexpected, and is not bound when absent.
     """
 
     name: str
@@ -24,8 +26,9 @@ class WeightDecl:
     role: str = "matrix"
     init: str = "normal"
     root: bool = False
+    optional: bool = False
 
     def under(self, prefix: str) -> "WeightDecl":
         if self.root:
             return self
-        return WeightDecl(prefix + self.name, self.shape, self.role, self.init, self.root)
+        return WeightDecl(prefix + self.name, self.shape, self.role, self.init, self.root, self.optional)

@@ -83,7 +83,7 @@ def load_weights(folder: str, decls: Sequence[WeightDecl], prefixes: Sequence[st
             raise WeightError(folder, [p + anchor for p in prefixes][-1:], [], [], other=[
                 f"anchor tensor {anchor!r} not found under any of the prefixes {list(prefixes)}"])
         full = {(d.name if d.root else prefix + d.name): d for d in decls}
-        missing = [n for n in full if n not in source.where]
+        missing = [n for n, d in full.items() if n not in source.where and not d.optional]
         unexpected = sorted(n for n in stored if n not in full)
         wrong_shape, wrong_dtype = [], []
         for n, d in full.items():
@@ -99,6 +99,8 @@ def load_weights(folder: str, decls: Sequence[WeightDecl], prefixes: Sequence[st
         out: Dict[str, torch.Tensor] = {}
         nonfinite: List[str] = []
         for i, (n, d) in enumerate(full.items()):
+            if n not in source.where:          # (optional, and the file leaves it out)
+                continue
             t = source.tensor(n)
             want = target_dtype(d.role, compute_dtype)
             dev = t.to(device=device, non_blocking=False)

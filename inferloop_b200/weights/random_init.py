@@ -91,7 +91,7 @@ def random_tensor(decl: WeightDecl, seed: int, dtype: torch.dtype,
         raise ValueError("integer tables have no random initialiser")
     if decl.init == "zeros":
         return torch.zeros(decl.shape, dtype=dtype, device=device)
-    if decl.init not in ("normal", "bias", "norm"):
+    if decl.init not in ("normal", "bias", "norm", "mix"):
         raise ValueError(f"unknown initialiser {decl.init!r}")
     count = 1
     for n in decl.shape:
@@ -99,6 +99,8 @@ def random_tensor(decl: WeightDecl, seed: int, dtype: torch.dtype,
     t = standard_normal(tensor_seed(seed, decl.name), count, device).view(tuple(decl.shape))
     if decl.init == "norm":
         t.mul_(0.1).add_(1.0)
+    elif decl.init == "mix":                 # coefficients of a learned mixture: around 1/2, away from 0 and 1
+        t.mul_(0.1).add_(0.5)
     else:
         t.mul_(0.02)
     return t.to(dtype)
