@@ -40,6 +40,7 @@ MODULES: Dict[str, List[str]] = {
     "sampling": [],
     "hyper": [],
     "moe": [],
+    "moe_gemm_tcgen05": [],
 }
 
 _LOCK = threading.Lock()

@@ -5,9 +5,10 @@
 //            weights (the chosen scores, optionally divided by their sum)
 //   plan     the (token, choice) pairs sorted by expert: every expert's rows start at a multiple
 //            of `block_rows`, so that a block of rows belongs to one expert; pos[pair] = row,
-//            row_pair[row] = pair or -1, block_expert[block] = expert or -1
-//   gather   a[row, :] = x[token of the row's pair, :] (times the pair's weight, when the weight
-//            multiplies the expert's input), zero for rows that hold no pair
+//            block_expert[block] = expert or -1
+//   gather   a[pos[pair], :] = x[token of the pair, :] (times the pair's weight, when the weight
+//            multiplies the expert's input); rows that hold no pair are left as they are: a row
+//            of a product depends on no other row, and nobody reads theirs
 //   combine  y[t, :] += sum over the token's choices, in choice order, of (weight *) out[pos, :]
 //            (+ gate[t] * shared[t, :], gate = sigmoid of a logit, for an expert every token uses)
 //
@@ -112,14 +113,13 @@ ILB_EXPORT int ilb_moe_route(const float* logits, int ld, int n_tokens, int expe
 // One CTA.  counts and offsets of the experts live in shared memory.
 __global__ void __launch_bounds__(1024)
 moe_plan_kernel(const int* __restrict__ choice, int n_pairs, int experts, int block_rows, int max_rows,
-                int* __restrict__ pos, int* __restrict__ row_pair, int* __restrict__ block_expert) {
+                int* __restrict__ pos, int* __restrict__ block_expert) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
   extern __shared__ int sh[];
   int* count = sh;                 // [experts]
   int* start = sh + experts;       // [experts + 1], in rows
   for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
-  for (int r = threadIdx.x; r < max_rows; r += blockDim.x) row_pair[r] = -1;
   for (int b = threadIdx.x; b < max_rows / block_rows; b += blockDim.x) block_expert[b] = -1;
   __syncthreads();
   for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
@@ -141,9 +141,7 @@ moe_plan_kernel(const int* __restrict__ choice, int n_pairs, int experts, int bl
   for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
     const int e = choice[p];
     if (pos[p] < 0) continue;
-    const int row = start[e] + pos[p];
-    pos[p] = row;
-    row_pair[row] = p;
+    pos[p] = start[e] + pos[p];
   }
 }
 
@@ -156,9 +154,9 @@ static inline long long plan_rows(long long n_pairs, int experts, int block_rows
 }
 ILB_EXPORT long long ilb_moe_plan_rows(long long n_pairs, int experts, int block_rows) { return plan_rows(n_pairs, experts, block_rows); }
 
-// choice: [n_pairs]; pos: [n_pairs]; row_pair: [max_rows]; block_expert: [max_rows / block_rows];
+// choice: [n_pairs]; pos: [n_pairs]; block_expert: [max_rows / block_rows];
 // max_rows >= ilb_moe_plan_rows(n_pairs, experts, block_rows), a multiple of block_rows.
-ILB_EXPORT int ilb_moe_plan(const int* choice, int n_pairs, int experts, int block_rows, int max_rows, int* pos, int* row_pair,
+ILB_EXPORT int ilb_moe_plan(const int* choice, int n_pairs, int experts, int block_rows, int max_rows, int* pos,
                             int* block_expert, cudaStream_t stream) {
   ILB_REQUIRE(n_pairs >= 0 && experts > 0 && block_rows > 0, "moe_plan: bad sizes");
   ILB_REQUIRE(max_rows % block_rows == 0 && max_rows >= plan_rows(n_pairs, experts, block_rows), "moe_plan: %d rows are too few",
@@ -166,23 +164,20 @@ ILB_EXPORT int ilb_moe_plan(const int* choice, int n_pairs, int experts, int blo
   ILB_REQUIRE((size_t)(2 * experts + 1) * sizeof(int) <= 48 * 1024, "moe_plan: too many experts");
   if (n_pairs == 0) return 0;
   ilb::launch(moe_plan_kernel, dim3(1), dim3(1024), (size_t)(2 * experts + 1) * sizeof(int), stream, choice, n_pairs, experts,
-              block_rows, max_rows, pos, row_pair, block_expert);
+              block_rows, max_rows, pos, block_expert);
   return check_launch("moe_plan");
 }
 
 template <typename T>
 __global__ void __launch_bounds__(128)
-moe_gather_kernel(const T* __restrict__ x, const float* __restrict__ weight, const int* __restrict__ row_pair, int top, int width,
+moe_gather_kernel(const T* __restrict__ x, const float* __restrict__ weight, const int* __restrict__ pos, int top, int width,
                   T* __restrict__ out) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
-  const int row = blockIdx.x;
-  const int p = row_pair[row];
+  const int p = blockIdx.x;
+  const int row = pos[p];
+  if (row < 0) return;
   T* o = out + (size_t)row * width;
-  if (p < 0) {
-    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_float<T>(0.f);
-    return;
-  }
   const T* src = x + (size_t)(p / top) * width;
   if (weight == nullptr) {
     for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = src[i];
@@ -192,15 +187,16 @@ moe_gather_kernel(const T* __restrict__ x, const float* __restrict__ weight, con
   }
 }
 
-// x: [T, width]; out: [rows, width]; weight (may be null): [n_pairs].
-ILB_EXPORT int ilb_moe_gather(const void* x, int dtype, const float* weight, const int* row_pair, int rows, int top, int width,
+// x: [T, width]; pos: [n_pairs] (pair t * top + j belongs to token t); out: [rows, width];
+// weight (may be null): [n_pairs].
+ILB_EXPORT int ilb_moe_gather(const void* x, int dtype, const float* weight, const int* pos, int n_pairs, int top, int width,
                               void* out, cudaStream_t stream) {
-  ILB_REQUIRE(rows >= 0 && top > 0 && width > 0, "moe_gather: bad sizes");
-  if (rows == 0) return 0;
+  ILB_REQUIRE(n_pairs >= 0 && top > 0 && width > 0, "moe_gather: bad sizes");
+  if (n_pairs == 0) return 0;
   if (dtype == kF32)
-    ilb::launch(moe_gather_kernel<float>, dim3(rows), dim3(128), 0, stream, (const float*)x, weight, row_pair, top, width, (float*)out);
+    ilb::launch(moe_gather_kernel<float>, dim3(n_pairs), dim3(128), 0, stream, (const float*)x, weight, pos, top, width, (float*)out);
   else if (dtype == kBF16)
-    ilb::launch(moe_gather_kernel<__nv_bfloat16>, dim3(rows), dim3(128), 0, stream, (const __nv_bfloat16*)x, weight, row_pair, top,
+    ilb::launch(moe_gather_kernel<__nv_bfloat16>, dim3(n_pairs), dim3(128), 0, stream, (const __nv_bfloat16*)x, weight, pos, top,
                 width, (__nv_bfloat16*)out);
   else
     return fail("moe_gather: unknown dtype %d", dtype);

@@ -1,0 +1,273 @@
+// Grouped bfloat16 matrix product on the tcgen05 tensor cores: the experts of a routed
+// feed-forward over rows that are sorted by expert.
+//
+//     out[rows of block b, :] = A[rows of block b, :] * W[group[b]]^T        (block = 128 rows)
+//
+// A is [rows, K] with every block of 128 rows belonging to one group (csrc/moe.cu deals the
+// rows), W is [groups, N, K], group[b] < 0 marks a block that holds no rows and is skipped.
+// One CTA computes one 128 x 128 tile: D[128 rows x 128 weight rows] accumulates in tensor
+// memory over K; warp 0 (one lane) streams the operands by TMA (cp.async.bulk.tensor, 128-byte
+// swizzle, no multicast) through a ring of three stages, warp 1 (one lane) issues tcgen05.mma
+// and commits, warps 2-5 read the accumulator with tcgen05.ld and write the rows out.  Two CTAs
+// fit an SM, so one tile's write-out runs under the other's products.  The weight tile of group
+// g starts at row g * N + n0 of the stacked matrix; columns past N are not written, so a tile
+// that reaches into the next group's rows (or past the end, where TMA fills zeros) is harmless.
+// With the SwiGLU epilogue W holds blocks of 64 gate rows followed by their 64 up rows, a tile is
+// one such pair, and out[:, n0/2 .. n0/2 + 63] = silu(gate) * up, so the [rows, 2 I] intermediate
+// is never written.  Every mbarrier wait is bounded; on expiry the kernel raises the error flag,
+// lets its other warps leave their waits, frees its tensor memory and returns.
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+#include "common.cuh"
+#include "sm100.cuh"
+
+using namespace ilb;
+
+namespace {
+
+constexpr int kBlockK = 64;             // bf16 elements per K block = one 128-byte swizzle row
+constexpr int kRows = 128;              // rows of A per tile = MMA M
+constexpr int kBN = 128;                // weight rows per tile = MMA N
+constexpr int kStages = 3;
+constexpr uint32_t kBytesA = kRows * kBlockK * 2, kBytesB = kBN * kBlockK * 2, kStageBytes = kBytesA + kBytesB;
+constexpr uint32_t kTmemCols = 128;
+constexpr size_t kSmem = (size_t)kStages * kStageBytes + 1024 + (2 * kStages + 4) * 8;
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+
+// K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// D = 32-bit, A and B = bfloat16, both K-major.
+__host__ __device__ constexpr uint32_t instr_desc(int mma_m, int mma_n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(mma_n >> 3) << 17) | ((uint32_t)(mma_m >> 4) << 24);
+}
+
+struct Params {
+  void* out;                 // [rows, N] (SwiGLU: [rows, N / 2]), bf16 or f32
+  const int* block_group;    // [rows / 128]
+  int* error_flag;
+  int N, K, ldo, k_blocks;
+  int swiglu, out_f32;
+};
+
+__global__ void __launch_bounds__(192, 2)
+moe_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const Params p) {
+  pdl_launch_dependents();
+  pdl_wait();                                    // the rows and their groups are the preceding kernels' work
+  const int b = blockIdx.y;
+  const int g = p.block_group[b];
+  if (g < 0) return;                             // (the whole CTA, before anything is set up)
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * kStages, tfull = empty0 + 8 * kStages;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * kStages + 1);
+  volatile int* failed = reinterpret_cast<volatile int*>(bars + 2 * kStages + 2);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * kBN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    mbar_init(tfull, 1);
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {                             // ---- TMA producer
+      bool ok = true;
+      for (int it = 0; it < p.k_blocks; ++it) {
+        const uint32_t s = it % kStages;
+        if (it >= kStages) {
+          ok = mbar_wait(empty0 + 8 * s, ((it / kStages) - 1) & 1);
+          if (!ok) break;
+        }
+        const uint32_t dst = base + s * kStageBytes;
+        mbar_expect_tx(full0 + 8 * s, kStageBytes);
+        tma_load_2d(dst, &map_a, full0 + 8 * s, it * kBlockK, b * kRows);
+        tma_load_2d(dst + kBytesA, &map_w, full0 + 8 * s, it * kBlockK, g * p.N + n0);
+      }
+      if (!ok) { *failed = 1; if (p.error_flag) *p.error_flag = 1; }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {                             // ---- MMA issuer
+      constexpr uint32_t idesc = instr_desc(kRows, kBN);
+      bool ok = true;
+      for (int it = 0; it < p.k_blocks; ++it) {
+        const uint32_t s = it % kStages;
+        ok = mbar_wait(full0 + 8 * s, (it / kStages) & 1);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t a = base + s * kStageBytes;
+        const uint64_t da = smem_desc(a), db = smem_desc(a + kBytesA);
+#pragma unroll
+        for (int k = 0; k < kBlockK / 16; ++k) mma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (it > 0 || k > 0) ? 1u : 0u);
+        tcgen05_commit(empty0 + 8 * s);          // the stage is free once these products have read it
+      }
+      if (!ok) { *failed = 1; if (p.error_flag) *p.error_flag = 1; }
+      tcgen05_commit(tfull);                     // arrives when every product issued so far is complete
+    }
+  } else {
+    // ---- write-out: warps 2..5 own tensor-memory lanes 32 (warp & 3) .. + 31, one row each
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    if (!mbar_wait(tfull, 0)) { *failed = 1; if (p.error_flag) *p.error_flag = 1; }
+    tcgen05_fence_after();
+    if (*failed == 0) {
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+      const size_t out_row = (size_t)(b * kRows + row) * p.ldo;
+      if (p.swiglu) {
+        const int c0 = n0 / 2;                   // the tile's 64 output columns
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          float gt[32], up[32];
+          tmem_load_32(taddr + 32 * half, gt);
+          tmem_load_32(taddr + 64 + 32 * half, up);
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = silu_mul(gt[j], up[j]);
+          const int c = c0 + 32 * half;
+          if (p.out_f32) {
+            float* o = (float*)p.out + out_row + c;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) if (c + j < p.N / 2) o[j] = v[j];
+          } else {
+            __nv_bfloat16* o = (__nv_bfloat16*)p.out + out_row + c;
+            if (c + 32 <= p.N / 2 && p.ldo % 8 == 0 && ((uintptr_t)p.out % 16 == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8)
+                *reinterpret_cast<uint4*>(o + j) = make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]),
+                                                              pack_bf16(v[j + 4], v[j + 5]), pack_bf16(v[j + 6], v[j + 7]));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (c + j < p.N / 2) o[j] = __float2bfloat16_rn(v[j]);
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int c0 = 0; c0 < kBN; c0 += 32) {
+          float v[32];
+          tmem_load_32(taddr + c0, v);
+          const int c = n0 + c0;
+          if (c >= p.N) continue;
+          if (p.out_f32) {
+            float* o = (float*)p.out + out_row + c;
+            if (c + 32 <= p.N && p.ldo % 4 == 0 && ((uintptr_t)p.out % 16 == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (c + j < p.N) o[j] = v[j];
+            }
+          } else {
+            __nv_bfloat16* o = (__nv_bfloat16*)p.out + out_row + c;
+            if (c + 32 <= p.N && p.ldo % 8 == 0 && ((uintptr_t)p.out % 16 == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8)
+                *reinterpret_cast<uint4*>(o + j) = make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]),
+                                                              pack_bf16(v[j + 4], v[j + 5]), pack_bf16(v[j + 6], v[j + 7]));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (c + j < p.N) o[j] = __float2bfloat16_rn(v[j]);
+            }
+          }
+        }
+      }
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+struct MapKey {
+  const void* ptr; long long rows; int cols, ld, box_rows;
+  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = std::hash<const void*>()(k.ptr) * 1000003u ^ std::hash<long long>()(k.rows);
+    for (int v : {k.cols, k.ld, k.box_rows}) h = h * 1000003u ^ std::hash<int>()(v);
+    return h;
+  }
+};
+
+// A [rows, cols] bf16 matrix with leading dimension ld (elements); box = [box_rows, 64].
+int make_map(CUtensorMap* out, const void* ptr, long long rows, int cols, int ld, int box_rows) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  const MapKey key{ptr, rows, cols, ld, box_rows};
+  std::lock_guard<std::mutex> guard(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return 0; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail("moe_gemm: cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("moe_gemm: cuTensorMapEncodeTiled failed with code %d (rows %lld cols %d ld %d)", (int)r, rows, cols, ld);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return 0;
+}
+
+}  // namespace
+
+ILB_EXPORT int ilb_moe_gemm_tc_block_rows() { return kRows; }
+
+// Whether these sizes meet the TMA rules (rows of 16 bytes, 16-byte bases).
+ILB_EXPORT int ilb_moe_gemm_tc_supported(int N, int K, int lda, int swiglu) {
+  return (K % 8 == 0 && lda % 8 == 0 && N > 0 && (!swiglu || N % 128 == 0)) ? 1 : 0;
+}
+
+// A: [rows, K] bf16 (leading dimension lda); W: [groups, N, K] bf16, contiguous; out: [rows, N]
+// (with swiglu: [rows, N / 2]) bf16 or f32 with leading dimension ldo; block_group: [rows / 128].
+ILB_EXPORT int ilb_moe_gemm_tc(const void* A, const void* W, void* out, int out_f32, int rows, int groups, int N, int K, int lda,
+                               int ldo, int swiglu, const int* block_group, int* error_flag, cudaStream_t stream) {
+  ILB_REQUIRE(rows >= 0 && groups > 0 && N > 0 && K > 0, "moe_gemm: bad sizes rows=%d groups=%d N=%d K=%d", rows, groups, N, K);
+  ILB_REQUIRE(rows % kRows == 0 && rows / kRows <= 65535, "moe_gemm: rows must come in blocks of %d (at most 65535 blocks)", kRows);
+  ILB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && lda >= K && ((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0),
+              "moe_gemm: operands must have rows of whole 16 bytes on 16-byte boundaries");
+  ILB_REQUIRE(!swiglu || N % 128 == 0, "moe_gemm: the SwiGLU epilogue needs gate and up rows in blocks of 64");
+  ILB_REQUIRE(ldo >= (swiglu ? N / 2 : N), "moe_gemm: output rows too short");
+  ILB_REQUIRE(block_group != nullptr, "moe_gemm: needs the group of every block of rows");
+  ILB_REQUIRE((long long)groups * N < 2147483647LL, "moe_gemm: too many weight rows");
+  if (rows == 0) return 0;
+  static OncePerDevice once;
+  if (once.first() &&
+      cudaFuncSetAttribute(moe_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) != cudaSuccess) {
+    once.forget();
+    return fail("moe_gemm: cannot reserve %zu bytes of shared memory", kSmem);
+  }
+  CUtensorMap ma, mw;
+  if (make_map(&ma, A, rows, K, lda, kRows)) return -1;
+  if (make_map(&mw, W, (long long)groups * N, K, K, kBN)) return -1;
+  Params p;
+  p.out = out; p.block_group = block_group; p.error_flag = error_flag;
+  p.N = N; p.K = K; p.ldo = ldo; p.k_blocks = (K + kBlockK - 1) / kBlockK;
+  p.swiglu = swiglu ? 1 : 0; p.out_f32 = out_f32 ? 1 : 0;
+  ilb::launch(moe_gemm_kernel, dim3((N + kBN - 1) / kBN, rows / kRows), dim3(192), kSmem, stream, ma, mw, p);
+  return check_launch("moe_gemm_tc");
+}
+
+ILB_DEFINE_LAST_ERROR()

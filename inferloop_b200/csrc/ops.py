@@ -189,22 +189,25 @@ def moe_route(logits: torch.Tensor, experts: int, top: int, softmax: bool, renor
           _i(1 if renormalize else 0), _ptr(choice), _ptr(weight), _stream(logits))
 
 
-def moe_plan(choice: torch.Tensor, experts: int, block_rows: int, pos: torch.Tensor, row_pair: torch.Tensor,
-             block_expert: torch.Tensor) -> None:
-    for t, w in ((choice, "choice"), (pos, "pos"), (row_pair, "row_pair"), (block_expert, "block_expert")):
+def moe_plan(choice: torch.Tensor, experts: int, block_rows: int, pos: torch.Tensor, block_expert: torch.Tensor) -> None:
+    """pos[pair] = the pair's row once the pairs are sorted by expert with every expert's rows
+    starting at a multiple of `block_rows`; block_expert[b] = the expert of rows b * block_rows
+    ..., or -1."""
+    for t, w in ((choice, "choice"), (pos, "pos"), (block_expert, "block_expert")):
         _need(t, "moe " + w, torch.int32)
-    rows = row_pair.numel()
-    if pos.numel() != choice.numel() or block_expert.numel() * block_rows != rows:
+    rows = block_expert.numel() * block_rows
+    if pos.numel() != choice.numel():
         raise KernelError("moe_plan: shapes do not agree")
-    _call("moe", "ilb_moe_plan", _ptr(choice), _i(choice.numel()), _i(experts), _i(block_rows), _i(rows), _ptr(pos), _ptr(row_pair),
+    _call("moe", "ilb_moe_plan", _ptr(choice), _i(choice.numel()), _i(experts), _i(block_rows), _i(rows), _ptr(pos),
           _ptr(block_expert), _stream(choice))
 
 
-def moe_gather(x: torch.Tensor, weight: Optional[torch.Tensor], row_pair: torch.Tensor, top: int, out: torch.Tensor) -> None:
-    _need(x, "moe x"); _need(out, "moe rows", x.dtype); _need(weight, "moe weight", torch.float32); _need(row_pair, "moe row_pair", torch.int32)
-    if out.shape[0] != row_pair.numel() or out.shape[1] != x.shape[1]:
+def moe_gather(x: torch.Tensor, weight: Optional[torch.Tensor], pos: torch.Tensor, top: int, out: torch.Tensor) -> None:
+    """out[pos[p]] = (weight[p] *) x[p // top] for every pair p; other rows of `out` are left alone."""
+    _need(x, "moe x"); _need(out, "moe rows", x.dtype); _need(weight, "moe weight", torch.float32); _need(pos, "moe pos", torch.int32)
+    if pos.numel() != x.shape[0] * top or out.shape[1] != x.shape[1]:
         raise KernelError("moe_gather: shapes do not agree")
-    _call("moe", "ilb_moe_gather", _ptr(x), _i(_code(x)), _ptr(weight), _ptr(row_pair), _i(out.shape[0]), _i(top), _i(x.shape[1]),
+    _call("moe", "ilb_moe_gather", _ptr(x), _i(_code(x)), _ptr(weight), _ptr(pos), _i(pos.numel()), _i(top), _i(x.shape[1]),
           _ptr(out), _stream(x))
 
 
@@ -228,6 +231,33 @@ def moe_combine(routed: torch.Tensor, pos: torch.Tensor, weight: Optional[torch.
 
 
 GROUP_ROWS_SIMT = 16       # rows of a block of the grouped exact product (ilb_gemm_simt_group_rows)
+GROUP_ROWS_TC = 128        # rows of a block of the grouped tensor-core product (ilb_moe_gemm_tc_block_rows)
+
+
+def moe_gemm_tc_eligible(a: torch.Tensor, w: torch.Tensor, swiglu: bool = False) -> bool:
+    """bfloat16 operands whose rows are multiples of 16 bytes (TMA's rule); gate and up rows in
+    blocks of 64 for the SwiGLU epilogue."""
+    return (TC_ENABLED and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0
+            and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and (not swiglu or w.shape[1] % 128 == 0))
+
+
+def moe_gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, block_group: torch.Tensor, swiglu: bool = False) -> None:
+    """out[rows of block b] = a[rows of block b] @ w[block_group[b]].T on tcgen05 tensor cores for
+    blocks of 128 rows (moe_gemm_tcgen05.cu); with `swiglu`, w holds blocks of 64 gate rows followed
+    by their 64 up rows and out is [rows, N / 2] = silu(gate) * up."""
+    _need(a, "moe gemm a", torch.bfloat16); _need(w, "moe gemm w", torch.bfloat16); _need(out, "moe gemm out")
+    _need(block_group, "moe gemm groups", torch.int32)
+    M, K = a.shape
+    if w.dim() != 3 or w.shape[2] != K or block_group.numel() * GROUP_ROWS_TC != M:
+        raise KernelError(f"moe_gemm_tc: shapes do not agree: a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    N = w.shape[1]
+    if tuple(out.shape) != (M, N // 2 if swiglu else N) or out.dtype not in (torch.float32, torch.bfloat16):
+        raise KernelError(f"moe_gemm_tc: output {tuple(out.shape)} {out.dtype} does not fit")
+    st = _tc_state(a.device)
+    _call("moe_gemm_tcgen05", "ilb_moe_gemm_tc", _ptr(a), _ptr(w), _ptr(out), _i(1 if out.dtype == torch.float32 else 0), _i(M),
+          _i(w.shape[0]), _i(N), _i(K), _i(a.stride(0)), _i(out.stride(0)), _i(1 if swiglu else 0), _ptr(block_group),
+          _ptr(st.error), _stream(out))
 
 
 def gemm_simt_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, block_group: torch.Tensor) -> None:

@@ -13,7 +13,10 @@ The experts' matrices are stacked at load into [experts, 2 I, H] (gate rows, the
 padded so that a block of rows belongs to one expert (csrc/moe.cu), gathers the inputs into
 that order, runs the two grouped products over it, and adds each token's rows back in choice
 order together with the shared expert.  No size depends on the routing, so decode steps can
-be replayed as recorded graphs.  The router's and the gate's logits come from one exact
+be replayed as recorded graphs.  On the bfloat16 path, when I is a multiple of 64, the grouped
+products run on the tcgen05 tensor cores in blocks of 128 rows (csrc/moe_gemm_tcgen05.cu) with
+gate and up rows interleaved in blocks of 64 and silu(gate) * up taken in the first product's
+epilogue, as the dense feed-forward does; otherwise they are the exact product in blocks of 16.  The router's and the gate's logits come from one exact
 32-bit product over the rows [W_router; W_gate].
 """
 from __future__ import annotations
@@ -64,6 +67,7 @@ class RoutedExperts(FeedForward):
             self.shared = SwiGLU(PartSpec.make("swiglu", hidden_size=self.hidden, intermediate_size=self.shared_inter,
                                                names=tuple(spec.get("shared_names", ()))), ctx, self.names["shared_prefix"])
         self.w_router = self.w_gate_up = self.w_down = None
+        self.fused = False          # gate/up rows interleaved for the tensor-core product's SwiGLU epilogue
 
     # ------------------------------------------------------------------ weights
     def declare_weights(self) -> List[WeightDecl]:
@@ -82,19 +86,31 @@ class RoutedExperts(FeedForward):
         n = self.names
         rows = [tensors[n["router"]]] + ([tensors[n["shared_gate"]]] if self.shared_gate else [])
         self.w_router = torch.cat(rows, dim=0).contiguous()
-        self.w_gate_up = torch.stack([torch.cat([tensors[n["gate"].format(e=e)], tensors[n["up"].format(e=e)]], dim=0)
-                                      for e in range(self.experts)]).contiguous()
+        gates = [tensors[n["gate"].format(e=e)] for e in range(self.experts)]
+        ups = [tensors[n["up"].format(e=e)] for e in range(self.experts)]
+        self.fused = gates[0].dtype == torch.bfloat16 and self.inter % 64 == 0 and self.hidden % 8 == 0
+        if self.fused:
+            blocks = self.inter // 64
+            self.w_gate_up = torch.stack([
+                torch.stack([g.view(blocks, 64, self.hidden), u.view(blocks, 64, self.hidden)], dim=1).reshape(2 * self.inter, self.hidden)
+                for g, u in zip(gates, ups)]).contiguous()
+        else:
+            self.w_gate_up = torch.stack([torch.cat([g, u], dim=0) for g, u in zip(gates, ups)]).contiguous()
         self.w_down = torch.stack([tensors[n["down"].format(e=e)] for e in range(self.experts)]).contiguous()
         if self.shared is not None:
             self.shared.bind(tensors)
 
+    def _block_rows(self) -> int:
+        fused = self.ctx.dtype == torch.bfloat16 and self.inter % 64 == 0 and self.hidden % 8 == 0
+        return ops.GROUP_ROWS_TC if fused else ops.GROUP_ROWS_SIMT
+
     def _rows(self, tokens: int) -> int:
-        return ops.moe_plan_rows(tokens * self.top, self.experts, ops.GROUP_ROWS_SIMT)
+        return ops.moe_plan_rows(tokens * self.top, self.experts, self._block_rows())
 
     def scratch_bytes(self, tokens: int) -> int:
         size = torch.empty((), dtype=self.ctx.dtype).element_size()
         rows = self._rows(tokens)
-        own = rows * ((self.hidden + 3 * self.inter) * size + self.hidden * 4) + tokens * (self.experts + 1 + 3 * self.top) * 4 + rows * 8
+        own = rows * ((self.hidden + 3 * self.inter) * size + self.hidden * 4) + tokens * (self.experts + 1 + 3 * self.top) * 4 + rows * 4
         shared = (self.shared.scratch_bytes(tokens) + tokens * self.hidden * 4) if self.shared is not None else 0
         return own + shared
 
@@ -102,7 +118,7 @@ class RoutedExperts(FeedForward):
     def forward(self, x: torch.Tensor, residual: torch.Tensor, step) -> None:
         T, H, I, E, K = x.shape[0], self.hidden, self.inter, self.experts, self.top
         ws, dt = self.ctx.workspace, self.ctx.dtype
-        block = ops.GROUP_ROWS_SIMT
+        block = self._block_rows()
         rows = self._rows(T)
         ops.scope("feed_forward.router")
         logits = ws.buffer("moe.logits", (T, self.w_router.shape[0]), torch.float32)
@@ -111,18 +127,23 @@ class RoutedExperts(FeedForward):
         weight = ws.buffer("moe.weight", (T * K,), torch.float32)
         ops.moe_route(logits, E, K, self.score == "softmax", self.renormalize, choice, weight)
         pos = ws.buffer("moe.pos", (T * K,), torch.int32)
-        row_pair = ws.buffer("moe.row_pair", (rows,), torch.int32)
         block_expert = ws.buffer("moe.block_expert", (rows // block,), torch.int32)
-        ops.moe_plan(choice, E, block, pos, row_pair, block_expert)
+        ops.moe_plan(choice, E, block, pos, block_expert)
         ops.scope("feed_forward.experts")
         a = ws.buffer("moe.rows", (rows, H), dt)
-        ops.moe_gather(x, weight if self.weight_on == "input" else None, row_pair, K, a)
-        gate_up = ws.buffer("moe.gate_up", (rows, 2 * I), dt)
-        ops.gemm_simt_grouped(a, self.w_gate_up, gate_up, block_expert)
+        ops.moe_gather(x, weight if self.weight_on == "input" else None, pos, K, a)
         act = ws.buffer("moe.act", (rows, I), dt)
-        ops.silu_mul(gate_up, act)
         routed = ws.buffer("moe.routed", (rows, H), torch.float32)
-        ops.gemm_simt_grouped(act, self.w_down, routed, block_expert)
+        if self.fused:
+            if not (ops.moe_gemm_tc_eligible(a, self.w_gate_up, swiglu=True) and ops.moe_gemm_tc_eligible(act, self.w_down)):
+                raise ops.KernelError("routed experts: the interleaved weights need the tensor-core product, which refused this input")
+            ops.moe_gemm_tc(a, self.w_gate_up, act, block_expert, swiglu=True)
+            ops.moe_gemm_tc(act, self.w_down, routed, block_expert)
+        else:
+            gate_up = ws.buffer("moe.gate_up", (rows, 2 * I), dt)
+            ops.gemm_simt_grouped(a, self.w_gate_up, gate_up, block_expert)
+            ops.silu_mul(gate_up, act)
+            ops.gemm_simt_grouped(act, self.w_down, routed, block_expert)
         shared_out = None
         if self.shared is not None:
             ops.scope("feed_forward.shared_expert")

@@ -146,7 +146,7 @@ def write_safetensors(path: str, tensors: Mapping[str, torch.Tensor] | Iterable[
         fh.write(blob)
         for _, t in items:
             c = t.detach().cpu().contiguous()
-            fh.write(c.view(torch.uint8).numpy().tobytes() if c.numel() else b"")
+            fh.write(c.reshape(-1).view(torch.uint8).numpy().tobytes() if c.numel() else b"")    # (a scalar has no dimension to view)
 
 
 class TensorSource:
