@@ -3,6 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
                     [--config 8b|14b-mixed|32b-long] [--breakdown] [--kernels [attention|products]] [--further]
+                    [--sufolix [dense|moe]]
 
 One JSON line on stdout.  The default (`--config 8b`) is the headline: Qwen3-8B layer sizes,
 36 layers, batch 8, 1,024-token prompts; a "step" is one decode step of the whole batch.
@@ -27,6 +28,9 @@ sizes of `--config`: the prefill attention at several lengths, and the layer's m
 at several token counts beside `torch.matmul` on the same shapes (the library's plain product,
 for comparison only; it has no epilogue).  `--further` measures further sizes at the 8B layer
 sizes: decode at batches 16 to 256, a prompt of 32,768 tokens in portions, the 32-bit path.
+`--sufolix` measures the Sufolix decoder (several residual streams, its attention variants, routed experts) at
+two layer sizes, dense and routed, beside a Qwen3 model of equal width, heads, layers and active feed-forward size:
+decode at --batch, one 2,048-token prompt, and the per-op-class device time of both.
 Peaks come from MEASURED_PEAKS.json beside this file when present, else the fallback
 figures 6.65 TB/s and 1.59 PFLOP/s.  Weights (15 GB and more) exceed L2 (126 MB), so every
 step reads them from HBM: no L2 flush is needed between timed steps.
@@ -143,8 +147,26 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+def sufolix_numbers(cfg: dict):
+    """The same for a Sufolix configuration (nested keys): a routed layer counts the experts one token runs."""
+    W, V, L = cfg["width"], cfg["vocab"], len(cfg["layers"])
+    params, kv, attn = 0, 0, 0
+    for layer in cfg["layers"]:
+        m, f = layer["mixer"], layer["mlp"]
+        params += ((m["heads"] + m["kv_heads"]) * m["dim"] + m["kv_heads"] * m["vdim"] + m["heads"] * m["vdim"]) * W
+        if f is not None and f["kind"] == "dense":
+            params += 3 * W * f["ff"]
+        elif f is not None:
+            params += 3 * W * (f["router"]["top"] * f["expert"]["ff"] + (f.get("shared") or {}).get("ff", 0)) + W * (f["router"]["experts"] + 1)
+        kv += m["kv_heads"] * (m["dim"] + m["vdim"]) * 2
+        attn += 2 * m["heads"] * (m["dim"] + m["vdim"])
+    return {"layer_params": params / L, "head_params": V * W, "kv_bytes_per_token": kv, "attn_flops_per_pair": attn, "layers": L}
+
+
 def model_numbers(cfg: dict):
     """Parameters the matrix products of one token touch, and bytes of cache per token."""
+    if cfg.get("architecture") == "Sufolix":
+        return sufolix_numbers(cfg)
     H, I, V, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
     nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     per_layer = (nq + 2 * nkv) * d * H + nq * d * H + 3 * H * I
@@ -186,7 +208,7 @@ class Bench:
         self.gen = torch.Generator().manual_seed(seed)
 
     def prompts(self, n, length):
-        return self.torch.randint(0, self.cfg["vocab_size"], (n, length), generator=self.gen).tolist()
+        return self.torch.randint(0, self.cfg.get("vocab_size") or self.cfg["vocab"], (n, length), generator=self.gen).tolist()
 
     def prefill(self, ids, toks):
         """Every prompt in portions of `chunk`; returns each request's first drawn token."""
@@ -632,6 +654,61 @@ def run_further(args) -> dict:
     return out
 
 
+# ----------------------------------------------------------------------------- the Sufolix decoder beside Qwen3
+def sufolix_config(kind: str, layers: int, width: int, heads: int, kv_heads: int, dim: int, ff: int, experts: int, top: int,
+                   expert_ff: int, shared_ff: int, vocab: int, streams: int) -> dict:
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "v_mix": True,
+             "rot": {"base": 1000000.0, "dims": dim}}
+    mlp = ({"kind": "dense", "ff": ff} if kind == "dense" else
+           {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff}, "shared": {"ff": shared_ff}})
+    return {"architecture": "Sufolix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "streams": streams, "layers": [{"type": "attention", "mixer": dict(mixer), "mlp": dict(mlp)} for _ in range(layers)]}
+
+
+def run_sufolix(args) -> dict:
+    """Decode and prefill of the Sufolix decoder at layer sizes of a real model, dense and routed, each beside a
+    Qwen3 model of the same width, heads, layers and feed-forward size per token; with the device time of every op class."""
+    import torch
+    L, W, HQ, HK, D, V, S = args.layers if args.layers != FULL_LAYERS else 8, 2048, 16, 4, 128, 32768, 2
+    FF, E, TOP, EFF, SFF = 8192, 16, 2, 1408, 2816
+    which = ["dense", "moe"] if args.sufolix == "all" else [args.sufolix]
+    out = {"metric": "sufolix_vs_qwen3_equal_size", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic",
+           "steps": args.steps, "warmup": args.warmup, "batch": args.batch, "peaks": peaks(), "cases": {}}
+    for kind in which:
+        active_ff = FF if kind == "dense" else TOP * EFF + SFF
+        arms = {
+            "sufolix": sufolix_config(kind, L, W, HQ, HK, D, FF, E, TOP, EFF, SFF, V, S),
+            "qwen3": dict(_COMMON, num_hidden_layers=L, hidden_size=W, num_attention_heads=HQ, num_key_value_heads=HK, head_dim=D,
+                          intermediate_size=active_ff, vocab_size=V, max_position_embeddings=8192),
+        }
+        case = {}
+        for arm, cfg in arms.items():
+            pages = (args.batch * (PROMPT_LEN + args.steps + args.warmup + 64) + PREFILL_LEN) // PAGE + 64
+            bench = Bench(cfg, SEED, pages, max(args.batch, 8), 8192, PREFILL_LEN)
+            with ClockSampler() as clocks:
+                tps, ms, kernels, ctx = bench.decode_device(args.batch, args.steps, args.warmup, arm, PROMPT_LEN)
+            touched = bench.weight_bytes
+            if arm == "sufolix" and kind == "moe":      # a step reads the experts its tokens chose: at most batch * top of them
+                expert_bytes = 3 * W * EFF * 2
+                touched -= L * expert_bytes * max(0, E - min(E, args.batch * TOP))
+            step_bytes = touched + args.batch * ctx * bench.nums["kv_bytes_per_token"]
+            r = {"decode_tokens_per_s": round(tps, 1), "decode_ms_per_step": round(ms, 4), "kernels_per_step": kernels,
+                 "decode_frac_of_hbm": round(step_bytes / (ms / 1e3) / 1e9 / bench.pk["hbm_gbs"], 4),
+                 "weights_gb": round(bench.weight_bytes / 1e9, 3), "clocks": clocks.summary(),
+                 "prefill": bench.prefill_timed(PREFILL_LEN, 3, PREFILL_SAMPLES)}
+            if args.breakdown:
+                r["breakdown"] = bench.breakdown(args.batch, PROMPT_LEN, PREFILL_LEN)
+            case[arm] = r
+            del bench
+            torch.cuda.empty_cache()
+        case["sizes"] = {"layers": L, "width": W, "heads": HQ, "kv_heads": HK, "head_dim": D, "vocab": V, "streams": S,
+                         "feed_forward_per_token": active_ff, **({"experts": E, "top": TOP, "expert_ff": EFF, "shared_ff": SFF} if kind == "moe" else {})}
+        case["decode_ratio_sufolix_over_qwen3"] = round(case["sufolix"]["decode_tokens_per_s"] / case["qwen3"]["decode_tokens_per_s"], 4)
+        case["prefill_ratio_sufolix_over_qwen3"] = round(case["sufolix"]["prefill"]["value"] / case["qwen3"]["prefill"]["value"], 4)
+        out["cases"][kind] = case
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -646,6 +723,8 @@ def main() -> int:
     ap.add_argument("--further", action="store_true", help="further sizes: batches to 256, a 32,768-token prompt, the 32-bit path")
     ap.add_argument("--kernels", nargs="?", const="all", default=None, choices=["all", "attention", "products"],
                     help="time kernels alone at the layer sizes of --config")
+    ap.add_argument("--sufolix", nargs="?", const="all", default=None, choices=["all", "dense", "moe"],
+                    help="the Sufolix decoder beside a Qwen3 model of equal size (decode, prefill, op classes with --breakdown)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -663,6 +742,9 @@ def main() -> int:
         return 0
     if args.further:
         print(json.dumps(run_further(args)))
+        return 0
+    if args.sufolix:
+        print(json.dumps(run_sufolix(args)))
         return 0
     result = {"8b": run_8b, "14b-mixed": run_14b_mixed, "32b-long": run_32b_long}[args.config](args)
     print(json.dumps(result))

@@ -49,9 +49,9 @@ class HyperConnectionBlock(Block):
 
     def _stream_decls(self, q: int, optional: bool) -> List[WeightDecl]:
         p, S = self.hc_names[q], self.streams
-        return [WeightDecl(p + "in", (S,), "vector", "mix", optional=optional),
-                WeightDecl(p + "out", (S,), "vector", "mix", optional=optional),
-                WeightDecl(p + "mix", (S, S), "vector", "mix", optional=optional)]
+        return [WeightDecl(p + "in", (S,), "vector", "norm", optional=optional),
+                WeightDecl(p + "out", (S,), "vector", "norm", optional=optional),
+                WeightDecl(p + "mix", (S, S), "vector", "eye", optional=optional)]
 
     def declare_weights(self) -> List[WeightDecl]:
         out = self.norm1.declare_weights() + self.mixer.declare_weights() + self._stream_decls(0, False)

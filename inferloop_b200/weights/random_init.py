@@ -91,7 +91,7 @@ def random_tensor(decl: WeightDecl, seed: int, dtype: torch.dtype,
         raise ValueError("integer tables have no random initialiser")
     if decl.init == "zeros":
         return torch.zeros(decl.shape, dtype=dtype, device=device)
-    if decl.init not in ("normal", "bias", "norm", "mix"):
+    if decl.init not in ("normal", "bias", "norm", "mix", "eye"):
         raise ValueError(f"unknown initialiser {decl.init!r}")
     count = 1
     for n in decl.shape:
@@ -101,6 +101,8 @@ def random_tensor(decl: WeightDecl, seed: int, dtype: torch.dtype,
         t.mul_(0.1).add_(1.0)
     elif decl.init == "mix":                 # coefficients of a learned mixture: around 1/2, away from 0 and 1
         t.mul_(0.1).add_(0.5)
+    elif decl.init == "eye":                 # a square matrix near the identity
+        t.mul_(0.1).add_(torch.eye(decl.shape[0], decl.shape[1], dtype=t.dtype, device=t.device))
     else:
         t.mul_(0.02)
     return t.to(dtype)

@@ -276,8 +276,8 @@ def test_rotation_of_neighbours_norm_after_it_and_mixed_values(dtype, nq, nkv, d
     call(v_lambda=lam)
     want = (1 - 0.37) * v2.double().view(T, nkv, dv) + 0.37 * v
     assert_close(cached(vc, dv), want, tol, "mixed values in the cache")
-    # the stock order gives something else when the head is rotated only in part (norm before, pairs i / i + rd/2)
-    if rd < d:
+    # the stock pairing (i with i + rd/2) gives something else as soon as there are two pairs
+    if rd >= 4:
         ops.qk_norm_rope_cache(qkv.to(DEV), q_out, None, None, eps, rope, rd, positions.to(DEV), seq.to(DEV), table.to(DEV), page, kc,
                                vc, nq, nkv, d, dv, ops.NORM_UNWEIGHTED)
         assert (q_out.view(T, nq, d).double().cpu() - q_ref).abs().max() > 1e-2
