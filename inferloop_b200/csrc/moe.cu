@@ -1,5 +1,6 @@
 // Routed feed-forward ("mixture of experts"): what lies around the experts' matrix products.
 //
+//   logits   z[T, E (+ 1)] = x W_router^T in 32-bit (a skinny product: a warp per token)
 //   route    router logits z[T, E] (32-bit) -> scores (sigmoid of each logit, or softmax over the
 //            experts), the `top` best experts of every token (ties to the lower index) and their
 //            weights (the chosen scores, optionally divided by their sum)
@@ -27,6 +28,98 @@ __device__ __forceinline__ float sigmoid_stable(float x) {
   if (x >= 0.f) return 1.0f / (1.0f + expf(-x));
   const float e = expf(x);
   return e / (1.0f + e);
+}
+
+// Router logits: out[t, e] = x[t, :] . w[e, :] in 32-bit for a few rows of w (the experts, and a
+// gate's row riding along).  A warp owns one token and walks kLogitRows rows of w: lanes take
+// consecutive pieces of eight features; a piece is one chain of fused multiply-adds from zero,
+// the pieces of a lane are added with the rounding error of every addition carried along in a
+// second word (two-sum), and the lanes meet in a butterfly sum.  The order of a logit's sum
+// depends on the width alone, and its error stays near that of eight terms, not of the width.
+constexpr int kLogitRows = 4;
+
+template <typename T> struct Piece8;
+template <> struct Piece8<float> {
+  __device__ static __forceinline__ void load(const float* p, float (&f)[8]) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+};
+template <> struct Piece8<__nv_bfloat16> {
+  __device__ static __forceinline__ void load(const __nv_bfloat16* p, float (&f)[8]) {
+    const uint4 r = __ldg(reinterpret_cast<const uint4*>(p));
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u); }
+  }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_logits_kernel(const T* __restrict__ x, const T* __restrict__ w, float* __restrict__ out, int n_tokens, int rows, int width,
+                  int vec) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= n_tokens) return;
+  const T* xr = x + (size_t)t * width;
+  const int e0 = blockIdx.y * kLogitRows;
+  float acc[kLogitRows], lost[kLogitRows];
+#pragma unroll
+  for (int r = 0; r < kLogitRows; ++r) { acc[r] = 0.f; lost[r] = 0.f; }
+  auto add = [&](int r, float part) {
+    const float sum = __fadd_rn(acc[r], part);
+    const float bp = __fsub_rn(sum, acc[r]);
+    lost[r] = __fadd_rn(lost[r], __fadd_rn(__fsub_rn(acc[r], __fsub_rn(sum, bp)), __fsub_rn(part, bp)));
+    acc[r] = sum;
+  };
+  if (vec) {
+    for (int i = lane * 8; i < width; i += 256) {
+      float xv[8];
+      Piece8<T>::load(xr + i, xv);
+#pragma unroll
+      for (int r = 0; r < kLogitRows; ++r) {
+        if (e0 + r >= rows) break;
+        float wv[8];
+        Piece8<T>::load(w + (size_t)(e0 + r) * width + i, wv);
+        float part = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) part = fmaf(xv[k], wv[k], part);
+        add(r, part);
+      }
+    }
+  } else {
+    for (int i = lane; i < width; i += 32) {
+      const float xv = to_float(xr[i]);
+#pragma unroll
+      for (int r = 0; r < kLogitRows; ++r)
+        if (e0 + r < rows) add(r, __fmul_rn(xv, to_float(w[(size_t)(e0 + r) * width + i])));
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < kLogitRows; ++r) {
+    const float v = warp_sum(__fadd_rn(acc[r], lost[r]));
+    if (lane == 0 && e0 + r < rows) out[(size_t)t * rows + e0 + r] = v;
+  }
+}
+
+// x: [T, width], w: [rows, width], both of `dtype`; out: [T, rows] 32-bit.
+ILB_EXPORT int ilb_moe_logits(const void* x, const void* w, int dtype, float* out, int n_tokens, int rows, int width,
+                              cudaStream_t stream) {
+  ILB_REQUIRE(n_tokens >= 0 && rows > 0 && width > 0, "moe_logits: bad sizes");
+  ILB_REQUIRE((rows + kLogitRows - 1) / kLogitRows <= 65535, "moe_logits: too many rows");
+  if (n_tokens == 0) return 0;
+  const dim3 grid((n_tokens + 3) / 4, (rows + kLogitRows - 1) / kLogitRows);
+  const int vec = (width % 8 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0)) ? 1 : 0;
+  if (dtype == kF32)
+    ilb::launch(moe_logits_kernel<float>, grid, dim3(128), 0, stream, (const float*)x, (const float*)w, out, n_tokens, rows, width, vec);
+  else if (dtype == kBF16)
+    ilb::launch(moe_logits_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out,
+                n_tokens, rows, width, vec);
+  else
+    return fail("moe_logits: unknown dtype %d", dtype);
+  return check_launch("moe_logits");
 }
 
 // One warp per token.

@@ -1,15 +1,18 @@
 // Grouped bfloat16 matrix product on the tcgen05 tensor cores: the experts of a routed
 // feed-forward over rows that are sorted by expert.
 //
-//     out[rows of block b, :] = A[rows of block b, :] * W[group[b]]^T        (block = 128 rows)
+//     out[rows of block b, :] = A[rows of block b, :] * W[group[b]]^T        (block = 128 or 256 rows)
 //
-// A is [rows, K] with every block of 128 rows belonging to one group (csrc/moe.cu deals the
+// A is [rows, K] with every block of rows belonging to one group (csrc/moe.cu deals the
 // rows), W is [groups, N, K], group[b] < 0 marks a block that holds no rows and is skipped.
-// One CTA computes one 128 x 128 tile: D[128 rows x 128 weight rows] accumulates in tensor
-// memory over K; warp 0 (one lane) streams the operands by TMA (cp.async.bulk.tensor, 128-byte
-// swizzle, no multicast) through a ring of three stages, warp 1 (one lane) issues tcgen05.mma
-// and commits, warps 2-5 read the accumulator with tcgen05.ld and write the rows out.  Two CTAs
-// fit an SM, so one tile's write-out runs under the other's products.  The weight tile of group
+// One CTA computes one tile: D accumulates in tensor memory over K; warp 0 (one lane) streams
+// the operands by TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) through a ring of
+// three stages, warp 1 (one lane) issues tcgen05.mma and commits, warps 2-5 read the
+// accumulators with tcgen05.ld and write the rows out.  Two tile shapes: 128 rows x 128 weight
+// rows, two CTAs to an SM so that one tile's write-out runs under the other's products (few
+// rows per expert: the launch streams the chosen experts' weights); and 256 rows x 256 weight
+// rows (two 128-row accumulators that share every weight block, all 512 columns of tensor memory),
+// which halves the operand bytes per flop when experts have hundreds of rows.  The weight tile of group
 // g starts at row g * N + n0 of the stacked matrix; columns past N are not written, so a tile
 // that reaches into the next group's rows (or past the end, where TMA fills zeros) is harmless.
 // With the SwiGLU epilogue W holds blocks of 64 gate rows followed by their 64 up rows, a tile is
@@ -27,12 +30,12 @@ using namespace ilb;
 namespace {
 
 constexpr int kBlockK = 64;             // bf16 elements per K block = one 128-byte swizzle row
-constexpr int kRows = 128;              // rows of A per tile = MMA M
-constexpr int kBN = 128;                // weight rows per tile = MMA N
+constexpr int kRows = 128;              // rows of one accumulator = MMA M
 constexpr int kStages = 3;
-constexpr uint32_t kBytesA = kRows * kBlockK * 2, kBytesB = kBN * kBlockK * 2, kStageBytes = kBytesA + kBytesB;
-constexpr uint32_t kTmemCols = 128;
-constexpr size_t kSmem = (size_t)kStages * kStageBytes + 1024 + (2 * kStages + 4) * 8;
+constexpr uint32_t kBytesA = kRows * kBlockK * 2;
+// MS row blocks of 128 and BN weight rows per tile
+template <int MS, int BN> __host__ __device__ constexpr uint32_t stage_bytes() { return MS * kBytesA + BN * kBlockK * 2; }
+template <int MS, int BN> constexpr size_t smem_bytes() { return (size_t)kStages * stage_bytes<MS, BN>() + 1024 + (2 * kStages + 4) * 8; }
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
@@ -47,14 +50,42 @@ __host__ __device__ constexpr uint32_t instr_desc(int mma_m, int mma_n) {
 
 struct Params {
   void* out;                 // [rows, N] (SwiGLU: [rows, N / 2]), bf16 or f32
-  const int* block_group;    // [rows / 128]
+  const int* block_group;    // [rows / rows of a tile]
   int* error_flag;
   int N, K, ldo, k_blocks;
   int swiglu, out_f32;
 };
 
-__global__ void __launch_bounds__(192, 2)
+// 32 consecutive columns of one output row, from column c on; columns from `limit` on are not written.
+__device__ __forceinline__ void store32(const Params& p, size_t out_row, int c, int limit, const float (&v)[32]) {
+  if (p.out_f32) {
+    float* o = (float*)p.out + out_row + c;
+    if (c + 32 <= limit && p.ldo % 4 == 0 && ((uintptr_t)p.out % 16 == 0)) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) if (c + j < limit) o[j] = v[j];
+    }
+  } else {
+    __nv_bfloat16* o = (__nv_bfloat16*)p.out + out_row + c;
+    if (c + 32 <= limit && p.ldo % 8 == 0 && ((uintptr_t)p.out % 16 == 0)) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8)
+        *reinterpret_cast<uint4*>(o + j) = make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]),
+                                                      pack_bf16(v[j + 4], v[j + 5]), pack_bf16(v[j + 6], v[j + 7]));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) if (c + j < limit) o[j] = __float2bfloat16_rn(v[j]);
+    }
+  }
+}
+
+template <int MS, int BN>
+__global__ void __launch_bounds__(192, MS == 1 ? 2 : 1)
 moe_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const Params p) {
+  constexpr uint32_t kStageBytes = stage_bytes<MS, BN>();
+  constexpr uint32_t kTmemCols = MS * BN;          // 128 or 512: a power of two
   pdl_launch_dependents();
   pdl_wait();                                    // the rows and their groups are the preceding kernels' work
   const int b = blockIdx.y;
@@ -68,7 +99,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * kStages + 1);
   volatile int* failed = reinterpret_cast<volatile int*>(bars + 2 * kStages + 2);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * kBN;
+  const int n0 = blockIdx.x * BN;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
@@ -96,14 +127,15 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         const uint32_t dst = base + s * kStageBytes;
         mbar_expect_tx(full0 + 8 * s, kStageBytes);
-        tma_load_2d(dst, &map_a, full0 + 8 * s, it * kBlockK, b * kRows);
-        tma_load_2d(dst + kBytesA, &map_w, full0 + 8 * s, it * kBlockK, g * p.N + n0);
+#pragma unroll
+        for (int ms = 0; ms < MS; ++ms) tma_load_2d(dst + ms * kBytesA, &map_a, full0 + 8 * s, it * kBlockK, (b * MS + ms) * kRows);
+        tma_load_2d(dst + MS * kBytesA, &map_w, full0 + 8 * s, it * kBlockK, g * p.N + n0);
       }
       if (!ok) { *failed = 1; if (p.error_flag) *p.error_flag = 1; }
     }
   } else if (warp == 1) {
     if (lane == 0) {                             // ---- MMA issuer
-      constexpr uint32_t idesc = instr_desc(kRows, kBN);
+      constexpr uint32_t idesc = instr_desc(kRows, BN);
       bool ok = true;
       for (int it = 0; it < p.k_blocks; ++it) {
         const uint32_t s = it % kStages;
@@ -111,9 +143,13 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t a = base + s * kStageBytes;
-        const uint64_t da = smem_desc(a), db = smem_desc(a + kBytesA);
+        const uint64_t db = smem_desc(a + MS * kBytesA);
 #pragma unroll
-        for (int k = 0; k < kBlockK / 16; ++k) mma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (it > 0 || k > 0) ? 1u : 0u);
+        for (int ms = 0; ms < MS; ++ms) {
+          const uint64_t da = smem_desc(a + ms * kBytesA);
+#pragma unroll
+          for (int k = 0; k < kBlockK / 16; ++k) mma_bf16(tmem_base + ms * BN, da + 2 * k, db + 2 * k, idesc, (it > 0 || k > 0) ? 1u : 0u);
+        }
         tcgen05_commit(empty0 + 8 * s);          // the stage is free once these products have read it
       }
       if (!ok) { *failed = 1; if (p.error_flag) *p.error_flag = 1; }
@@ -126,63 +162,35 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (!mbar_wait(tfull, 0)) { *failed = 1; if (p.error_flag) *p.error_flag = 1; }
     tcgen05_fence_after();
     if (*failed == 0) {
-      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
-      const size_t out_row = (size_t)(b * kRows + row) * p.ldo;
-      if (p.swiglu) {
-        const int c0 = n0 / 2;                   // the tile's 64 output columns
+#pragma unroll 1
+      for (int ms = 0; ms < MS; ++ms) {
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + ms * BN;
+        const size_t out_row = (size_t)((b * MS + ms) * kRows + row) * p.ldo;
+        if (p.swiglu) {
+          // a pair of 64 gate rows and their 64 up rows gives 64 output columns
+#pragma unroll 1
+          for (int pair = 0; pair < BN / 128; ++pair) {
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          float gt[32], up[32];
-          tmem_load_32(taddr + 32 * half, gt);
-          tmem_load_32(taddr + 64 + 32 * half, up);
-          float v[32];
+            for (int half = 0; half < 2; ++half) {
+              const int c = n0 / 2 + pair * 64 + 32 * half;
+              if (c >= p.N / 2) continue;
+              float gt[32], up[32];
+              tmem_load_32(taddr + pair * 128 + 32 * half, gt);
+              tmem_load_32(taddr + pair * 128 + 64 + 32 * half, up);
+              float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = silu_mul(gt[j], up[j]);
-          const int c = c0 + 32 * half;
-          if (p.out_f32) {
-            float* o = (float*)p.out + out_row + c;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) if (c + j < p.N / 2) o[j] = v[j];
-          } else {
-            __nv_bfloat16* o = (__nv_bfloat16*)p.out + out_row + c;
-            if (c + 32 <= p.N / 2 && p.ldo % 8 == 0 && ((uintptr_t)p.out % 16 == 0)) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8)
-                *reinterpret_cast<uint4*>(o + j) = make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]),
-                                                              pack_bf16(v[j + 4], v[j + 5]), pack_bf16(v[j + 6], v[j + 7]));
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) if (c + j < p.N / 2) o[j] = __float2bfloat16_rn(v[j]);
+              for (int j = 0; j < 32; ++j) v[j] = silu_mul(gt[j], up[j]);
+              store32(p, out_row, c, p.N / 2, v);
             }
           }
-        }
-      } else {
-#pragma unroll
-        for (int c0 = 0; c0 < kBN; c0 += 32) {
-          float v[32];
-          tmem_load_32(taddr + c0, v);
-          const int c = n0 + c0;
-          if (c >= p.N) continue;
-          if (p.out_f32) {
-            float* o = (float*)p.out + out_row + c;
-            if (c + 32 <= p.N && p.ldo % 4 == 0 && ((uintptr_t)p.out % 16 == 0)) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) if (c + j < p.N) o[j] = v[j];
-            }
-          } else {
-            __nv_bfloat16* o = (__nv_bfloat16*)p.out + out_row + c;
-            if (c + 32 <= p.N && p.ldo % 8 == 0 && ((uintptr_t)p.out % 16 == 0)) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8)
-                *reinterpret_cast<uint4*>(o + j) = make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]),
-                                                              pack_bf16(v[j + 4], v[j + 5]), pack_bf16(v[j + 6], v[j + 7]));
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) if (c + j < p.N) o[j] = __float2bfloat16_rn(v[j]);
-            }
+        } else {
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            const int c = n0 + c0;
+            if (c >= p.N) break;
+            float v[32];
+            tmem_load_32(taddr + c0, v);
+            store32(p, out_row, c, p.N, v);
           }
         }
       }
@@ -233,7 +241,21 @@ int make_map(CUtensorMap* out, const void* ptr, long long rows, int cols, int ld
 
 }  // namespace
 
-ILB_EXPORT int ilb_moe_gemm_tc_block_rows() { return kRows; }
+template <int MS, int BN>
+static int launch_tiles(const void* A, const void* W, const Params& p, int rows, int groups, int lda, cudaStream_t stream) {
+  static OncePerDevice once;
+  constexpr size_t smem = smem_bytes<MS, BN>();
+  if (once.first() &&
+      cudaFuncSetAttribute(moe_gemm_kernel<MS, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    once.forget();
+    return fail("moe_gemm: cannot reserve %zu bytes of shared memory", smem);
+  }
+  CUtensorMap ma, mw;
+  if (make_map(&ma, A, rows, p.K, lda, kRows)) return -1;
+  if (make_map(&mw, W, (long long)groups * p.N, p.K, p.K, BN)) return -1;
+  ilb::launch(moe_gemm_kernel<MS, BN>, dim3((p.N + BN - 1) / BN, rows / (MS * kRows)), dim3(192), smem, stream, ma, mw, p);
+  return check_launch("moe_gemm_tc");
+}
 
 // Whether these sizes meet the TMA rules (rows of 16 bytes, 16-byte bases).
 ILB_EXPORT int ilb_moe_gemm_tc_supported(int N, int K, int lda, int swiglu) {
@@ -241,11 +263,13 @@ ILB_EXPORT int ilb_moe_gemm_tc_supported(int N, int K, int lda, int swiglu) {
 }
 
 // A: [rows, K] bf16 (leading dimension lda); W: [groups, N, K] bf16, contiguous; out: [rows, N]
-// (with swiglu: [rows, N / 2]) bf16 or f32 with leading dimension ldo; block_group: [rows / 128].
+// (with swiglu: [rows, N / 2]) bf16 or f32 with leading dimension ldo; block_group: [rows / block_rows],
+// block_rows = 128 or 256 (the tile is then 128 x 128 or 256 x 256).
 ILB_EXPORT int ilb_moe_gemm_tc(const void* A, const void* W, void* out, int out_f32, int rows, int groups, int N, int K, int lda,
-                               int ldo, int swiglu, const int* block_group, int* error_flag, cudaStream_t stream) {
+                               int ldo, int swiglu, const int* block_group, int block_rows, int* error_flag, cudaStream_t stream) {
   ILB_REQUIRE(rows >= 0 && groups > 0 && N > 0 && K > 0, "moe_gemm: bad sizes rows=%d groups=%d N=%d K=%d", rows, groups, N, K);
-  ILB_REQUIRE(rows % kRows == 0 && rows / kRows <= 65535, "moe_gemm: rows must come in blocks of %d (at most 65535 blocks)", kRows);
+  ILB_REQUIRE(block_rows == 128 || block_rows == 256, "moe_gemm: blocks of 128 or 256 rows, not %d", block_rows);
+  ILB_REQUIRE(rows % block_rows == 0 && rows / block_rows <= 65535, "moe_gemm: rows must come in blocks of %d (at most 65535 blocks)", block_rows);
   ILB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && lda >= K && ((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0),
               "moe_gemm: operands must have rows of whole 16 bytes on 16-byte boundaries");
   ILB_REQUIRE(!swiglu || N % 128 == 0, "moe_gemm: the SwiGLU epilogue needs gate and up rows in blocks of 64");
@@ -253,21 +277,12 @@ ILB_EXPORT int ilb_moe_gemm_tc(const void* A, const void* W, void* out, int out_
   ILB_REQUIRE(block_group != nullptr, "moe_gemm: needs the group of every block of rows");
   ILB_REQUIRE((long long)groups * N < 2147483647LL, "moe_gemm: too many weight rows");
   if (rows == 0) return 0;
-  static OncePerDevice once;
-  if (once.first() &&
-      cudaFuncSetAttribute(moe_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) != cudaSuccess) {
-    once.forget();
-    return fail("moe_gemm: cannot reserve %zu bytes of shared memory", kSmem);
-  }
-  CUtensorMap ma, mw;
-  if (make_map(&ma, A, rows, K, lda, kRows)) return -1;
-  if (make_map(&mw, W, (long long)groups * N, K, K, kBN)) return -1;
   Params p;
   p.out = out; p.block_group = block_group; p.error_flag = error_flag;
   p.N = N; p.K = K; p.ldo = ldo; p.k_blocks = (K + kBlockK - 1) / kBlockK;
   p.swiglu = swiglu ? 1 : 0; p.out_f32 = out_f32 ? 1 : 0;
-  ilb::launch(moe_gemm_kernel, dim3((N + kBN - 1) / kBN, rows / kRows), dim3(192), kSmem, stream, ma, mw, p);
-  return check_launch("moe_gemm_tc");
+  if (block_rows == 256) return launch_tiles<2, 256>(A, W, p, rows, groups, lda, stream);
+  return launch_tiles<1, 128>(A, W, p, rows, groups, lda, stream);
 }
 
 ILB_DEFINE_LAST_ERROR()

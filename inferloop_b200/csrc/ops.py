@@ -179,6 +179,14 @@ def moe_plan_rows(n_pairs: int, experts: int, block_rows: int) -> int:
     return -(-rows // block_rows) * block_rows
 
 
+def moe_logits(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, e] = x[t] . w[e] in 32-bit for the few rows of a router's matrix (same dtype as x)."""
+    _need(x, "router x"); _need(w, "router matrix", x.dtype); _need(out, "router logits", torch.float32)
+    if w.shape[1] != x.shape[1] or tuple(out.shape) != (x.shape[0], w.shape[0]):
+        raise KernelError("moe_logits: shapes do not agree")
+    _call("moe", "ilb_moe_logits", _ptr(x), _ptr(w), _i(_code(x)), _ptr(out), _i(x.shape[0]), _i(w.shape[0]), _i(x.shape[1]), _stream(x))
+
+
 def moe_route(logits: torch.Tensor, experts: int, top: int, softmax: bool, renormalize: bool,
               choice: torch.Tensor, weight: torch.Tensor) -> None:
     _need(logits, "router logits", torch.float32); _need(choice, "moe choice", torch.int32); _need(weight, "moe weight", torch.float32)
@@ -231,7 +239,8 @@ def moe_combine(routed: torch.Tensor, pos: torch.Tensor, weight: Optional[torch.
 
 
 GROUP_ROWS_SIMT = 16       # rows of a block of the grouped exact product (ilb_gemm_simt_group_rows)
-GROUP_ROWS_TC = 128        # rows of a block of the grouped tensor-core product (ilb_moe_gemm_tc_block_rows)
+GROUP_ROWS_TC = 128        # rows of a block of the grouped tensor-core product: 128 x 128 tiles, two CTAs to an SM
+GROUP_ROWS_TC_WIDE = 256   # or 256 x 256 tiles, when experts have hundreds of rows
 
 
 def moe_gemm_tc_eligible(a: torch.Tensor, w: torch.Tensor, swiglu: bool = False) -> bool:
@@ -242,14 +251,15 @@ def moe_gemm_tc_eligible(a: torch.Tensor, w: torch.Tensor, swiglu: bool = False)
             and (not swiglu or w.shape[1] % 128 == 0))
 
 
-def moe_gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, block_group: torch.Tensor, swiglu: bool = False) -> None:
+def moe_gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, block_group: torch.Tensor, swiglu: bool = False,
+                block_rows: int = GROUP_ROWS_TC) -> None:
     """out[rows of block b] = a[rows of block b] @ w[block_group[b]].T on tcgen05 tensor cores for
-    blocks of 128 rows (moe_gemm_tcgen05.cu); with `swiglu`, w holds blocks of 64 gate rows followed
-    by their 64 up rows and out is [rows, N / 2] = silu(gate) * up."""
+    blocks of 128 or 256 rows (moe_gemm_tcgen05.cu); with `swiglu`, w holds blocks of 64 gate rows
+    followed by their 64 up rows and out is [rows, N / 2] = silu(gate) * up."""
     _need(a, "moe gemm a", torch.bfloat16); _need(w, "moe gemm w", torch.bfloat16); _need(out, "moe gemm out")
     _need(block_group, "moe gemm groups", torch.int32)
     M, K = a.shape
-    if w.dim() != 3 or w.shape[2] != K or block_group.numel() * GROUP_ROWS_TC != M:
+    if w.dim() != 3 or w.shape[2] != K or block_group.numel() * block_rows != M:
         raise KernelError(f"moe_gemm_tc: shapes do not agree: a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
     N = w.shape[1]
     if tuple(out.shape) != (M, N // 2 if swiglu else N) or out.dtype not in (torch.float32, torch.bfloat16):
@@ -257,7 +267,7 @@ def moe_gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, block_group
     st = _tc_state(a.device)
     _call("moe_gemm_tcgen05", "ilb_moe_gemm_tc", _ptr(a), _ptr(w), _ptr(out), _i(1 if out.dtype == torch.float32 else 0), _i(M),
           _i(w.shape[0]), _i(N), _i(K), _i(a.stride(0)), _i(out.stride(0)), _i(1 if swiglu else 0), _ptr(block_group),
-          _ptr(st.error), _stream(out))
+          _i(block_rows), _ptr(st.error), _stream(out))
 
 
 def gemm_simt_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, block_group: torch.Tensor) -> None:

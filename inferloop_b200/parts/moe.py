@@ -14,10 +14,11 @@ padded so that a block of rows belongs to one expert (csrc/moe.cu), gathers the 
 that order, runs the two grouped products over it, and adds each token's rows back in choice
 order together with the shared expert.  No size depends on the routing, so decode steps can
 be replayed as recorded graphs.  On the bfloat16 path, when I is a multiple of 64, the grouped
-products run on the tcgen05 tensor cores in blocks of 128 rows (csrc/moe_gemm_tcgen05.cu) with
+products run on the tcgen05 tensor cores in blocks of 128 or 256 rows (csrc/moe_gemm_tcgen05.cu) with
 gate and up rows interleaved in blocks of 64 and silu(gate) * up taken in the first product's
-epilogue, as the dense feed-forward does; otherwise they are the exact product in blocks of 16.  The router's and the gate's logits come from one exact
-32-bit product over the rows [W_router; W_gate].
+epilogue, as the dense feed-forward does; otherwise they are the exact product in blocks of 16.
+The router's and the gate's logits come from one 32-bit product over the rows [W_router; W_gate]
+(a warp per token: the matrix has few rows).
 """
 from __future__ import annotations
 
@@ -100,12 +101,16 @@ class RoutedExperts(FeedForward):
         if self.shared is not None:
             self.shared.bind(tensors)
 
-    def _block_rows(self) -> int:
+    def _block_rows(self, tokens: int) -> int:
+        """Rows of a block of the sorted order: the exact product's 16, or the tensor-core
+        product's tile height, the wide tile once an expert gets a tile's worth of rows on average."""
         fused = self.ctx.dtype == torch.bfloat16 and self.inter % 64 == 0 and self.hidden % 8 == 0
-        return ops.GROUP_ROWS_TC if fused else ops.GROUP_ROWS_SIMT
+        if not fused:
+            return ops.GROUP_ROWS_SIMT
+        return ops.GROUP_ROWS_TC_WIDE if tokens * self.top >= self.experts * ops.GROUP_ROWS_TC_WIDE else ops.GROUP_ROWS_TC
 
     def _rows(self, tokens: int) -> int:
-        return ops.moe_plan_rows(tokens * self.top, self.experts, self._block_rows())
+        return ops.moe_plan_rows(tokens * self.top, self.experts, self._block_rows(tokens))
 
     def scratch_bytes(self, tokens: int) -> int:
         size = torch.empty((), dtype=self.ctx.dtype).element_size()
@@ -118,11 +123,11 @@ class RoutedExperts(FeedForward):
     def forward(self, x: torch.Tensor, residual: torch.Tensor, step) -> None:
         T, H, I, E, K = x.shape[0], self.hidden, self.inter, self.experts, self.top
         ws, dt = self.ctx.workspace, self.ctx.dtype
-        block = self._block_rows()
+        block = self._block_rows(T)
         rows = self._rows(T)
         ops.scope("feed_forward.router")
         logits = ws.buffer("moe.logits", (T, self.w_router.shape[0]), torch.float32)
-        ops.gemm_simt(x, self.w_router, logits)
+        ops.moe_logits(x, self.w_router, logits)
         choice = ws.buffer("moe.choice", (T * K,), torch.int32)
         weight = ws.buffer("moe.weight", (T * K,), torch.float32)
         ops.moe_route(logits, E, K, self.score == "softmax", self.renormalize, choice, weight)
@@ -137,8 +142,8 @@ class RoutedExperts(FeedForward):
         if self.fused:
             if not (ops.moe_gemm_tc_eligible(a, self.w_gate_up, swiglu=True) and ops.moe_gemm_tc_eligible(act, self.w_down)):
                 raise ops.KernelError("routed experts: the interleaved weights need the tensor-core product, which refused this input")
-            ops.moe_gemm_tc(a, self.w_gate_up, act, block_expert, swiglu=True)
-            ops.moe_gemm_tc(act, self.w_down, routed, block_expert)
+            ops.moe_gemm_tc(a, self.w_gate_up, act, block_expert, swiglu=True, block_rows=block)
+            ops.moe_gemm_tc(act, self.w_down, routed, block_expert, block_rows=block)
         else:
             gate_up = ws.buffer("moe.gate_up", (rows, 2 * I), dt)
             ops.gemm_simt_grouped(a, self.w_gate_up, gate_up, block_expert)

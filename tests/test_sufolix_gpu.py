@@ -151,6 +151,29 @@ def test_long_decoding_through_recorded_graphs(root, name, dtype):
         assert r.graphs.replays > 200
 
 
+@pytest.mark.parametrize("name,dtype", [("Q", "bfloat16"), ("R", "bfloat16"), ("S", "float32")])
+def test_a_long_prompt_whole_and_in_portions(root, name, dtype):
+    """900 tokens in one step (at Q's sizes the experts then run on the wide tiles, the attention
+    on two row blocks) against the same prompt in portions of 128 and 100: the logits at a position
+    do not depend on the cut.  Keys far back count: every tenth row is compared."""
+    from helpers import random_tokens
+    from inferloop_b200.engine import StepEntry
+    vocab = cases.CASES[name][0]["vocab"]
+    toks = random_tokens(900, vocab, 77)
+    want = list(range(5, 900, 10)) + [899]
+    r = runner_for(root, name, dtype, pages=-(-900 // cases.CASES[name][2]) + 2)
+    whole = r.step([StepEntry("w", toks, want)]).float().cpu().clone()
+    r.end("w")
+    for portion in (128, 100):
+        rows = []
+        for at in range(0, 900, portion):
+            part = toks[at:at + portion]
+            out = r.step([StepEntry("p", part, [w - at for w in want if at <= w < at + len(part)])])
+            rows.append(out.float().cpu().clone())
+        r.end("p")
+        assert_close(torch.cat(rows), whole, dtype, f"{name} portions of {portion} against the whole prompt")
+
+
 @pytest.mark.parametrize("name,dtype", [("P", "float32"), ("Q", "bfloat16"), ("R", "float32")])
 def test_greedy_generation_through_the_entry_point(root, name, dtype):
     from inferloop_b200 import Engine, SamplingParams
@@ -345,14 +368,27 @@ def test_routing_scores_choices_and_weights(experts, top, softmax, renorm):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("block", [16, 128])
-@pytest.mark.parametrize("T,experts,top,H,I", [(1, 4, 2, 64, 64), (9, 5, 2, 96, 128), (300, 8, 1, 256, 64), (77, 3, 3, 128, 192)])
+@pytest.mark.parametrize("T,rows,width", [(1, 3, 64), (9, 17, 2048), (130, 161, 96), (5, 8, 100), (33, 6, 4104)])
+def test_router_logits_are_32_bit_sums(dtype, T, rows, width):
+    from inferloop_b200.csrc import ops
+    g = torch.Generator().manual_seed(T + rows)
+    x = torch.randn(T, width, generator=g).to(dtype)
+    w = torch.randn(rows, width, generator=g).to(dtype)
+    out = torch.empty(T, rows, dtype=torch.float32, device=DEV)
+    ops.moe_logits(x.to(DEV), w.to(DEV), out)
+    assert_close(out, x.double() @ w.double().T, "float32", "router logits")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("block", [16, 128, 256])
+@pytest.mark.parametrize("T,experts,top,H,I", [(1, 4, 2, 64, 64), (9, 5, 2, 96, 128), (300, 8, 1, 256, 64), (77, 3, 3, 128, 192),
+                                               (700, 2, 2, 320, 384)])
 def test_sorted_rows_grouped_products_and_the_sum(dtype, block, T, experts, top, H, I):
-    """plan -> gather -> grouped product (exact in blocks of 16; on tensor cores in blocks of 128,
+    """plan -> gather -> grouped product (exact in blocks of 16; on tensor cores in blocks of 128 and 256,
     with and without the SwiGLU epilogue) -> combine, with weights on the input and on the output,
     against per-token products."""
     from inferloop_b200.csrc import ops
-    if block == 128 and dtype != torch.bfloat16:
+    if block >= 128 and dtype != torch.bfloat16:
         pytest.skip("the tensor-core product is bfloat16")
     g = torch.Generator().manual_seed(T + experts)
     x = torch.randn(T, H, generator=g).to(dtype)
@@ -376,7 +412,7 @@ def test_sorted_rows_grouped_products_and_the_sum(dtype, block, T, experts, top,
         if block == 16:
             ops.gemm_simt_grouped(a, w1.to(DEV), out, block_expert)
         else:
-            ops.moe_gemm_tc(a, w1.to(DEV), out, block_expert)
+            ops.moe_gemm_tc(a, w1.to(DEV), out, block_expert, block_rows=block)
         y = torch.zeros(T, I, dtype=torch.float32, device=DEV)
         shared = torch.randn(T, I, generator=g)
         gate = torch.randn(T, 3, generator=g)
@@ -390,11 +426,11 @@ def test_sorted_rows_grouped_products_and_the_sum(dtype, block, T, experts, top,
                 ref[t] += (xin @ w1[e].double().T) * (1.0 if weighted_input else wt)
             ref[t] += shared[t].double() / (1 + math.exp(-float(gate[t, 2])))
         assert_close(y, ref, "float32" if dtype == torch.float32 else "bfloat16", f"weighted_input={weighted_input}", bf16_rel_of_max=2e-3)
-    if block == 128 and I % 64 == 0:        # the SwiGLU epilogue: gate and up rows interleaved in blocks of 64
+    if block >= 128 and I % 64 == 0:        # the SwiGLU epilogue: gate and up rows interleaved in blocks of 64
         wg, wu = (torch.randn(experts, I, H, generator=g) * 0.2).to(dtype), (torch.randn(experts, I, H, generator=g) * 0.2).to(dtype)
         inter = torch.stack([wg.view(experts, I // 64, 64, H), wu.view(experts, I // 64, 64, H)], dim=2).reshape(experts, 2 * I, H).contiguous()
         act = torch.empty(rows, I, dtype=torch.bfloat16, device=DEV)
-        ops.moe_gemm_tc(a, inter.to(DEV), act, block_expert, swiglu=True)
+        ops.moe_gemm_tc(a, inter.to(DEV), act, block_expert, swiglu=True, block_rows=block)
         for t in range(0, T, max(1, T // 7)):
             e = int(choice[t, 0])
             xin = x[t].double()
