@@ -77,9 +77,18 @@ struct Params {
   // to write are null) and patched into the tile that holds their position.
   const __nv_bfloat16* qkv; int qkv_stride;
   const float* q_weight; const float* k_weight; float eps;
-  const float2* rope;                  // [tokens][D / 2] (cos, sin), rotation over the whole head
+  const float2* rope;                  // [tokens][rotary_dim / 2] (cos, sin)
   __nv_bfloat16* k_write; __nv_bfloat16* v_write;
+  // Variants of the input stage (bits of `mode`, as in qk_norm_rope.cu): 1 = the rotation pairs
+  // are neighbours (2i, 2i + 1), over the first rotary_dim elements; 2 = the norm follows the
+  // rotation; 4 = q and k are divided by their root mean square without a weight.  The stock
+  // pairing (i, i + D/2) rotates the whole head.  v_mode 1: the step's values are also kept in
+  // v_first [tokens][nkv * D]; 2: they become (1 - lambda) v + lambda v_first before they are cached.
+  int mode, rotary_dim, v_mode;
+  __nv_bfloat16* v_first; const float* v_lambda;
 };
+
+constexpr int kPairsInterleaved = 1, kNormAfterRotation = 2, kNormUnweighted = 4;
 
 // Address of the 16-byte piece `chunk` (0..7) of row `row` in a [rows][128 bytes] slice
 // written by TMA with the 128-byte swizzle (the slice starts on a 1024-byte boundary).
@@ -238,6 +247,87 @@ __device__ __forceinline__ void load_q_fused(uint32_t (&q)[D / 16][4], const __n
   }
 }
 
+// The same for the variants of the input stage (Params::mode): pairs of neighbours over the first
+// `rd` elements, the norm before or after the rotation, with or without a weight.
+template <int D>
+__device__ __forceinline__ void load_q_variant(uint32_t (&q)[D / 16][4], const __nv_bfloat16* row0, const __nv_bfloat16* row1,
+                                               const float* weight, float eps, const float2* cs, int lane, int mode, int rd) {
+  const int t = lane & 3;
+  const bool normed = weight != nullptr || (mode & kNormUnweighted);
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const __nv_bfloat16* row = r == 0 ? row0 : row1;
+    float x[D / 16][4];                                  // [kk][c, c+1, c+8, c+9], c = 16 kk + 2 t
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      const int c = kk * 16 + 2 * t;
+      __nv_bfloat162 a = __floats2bfloat162_rn(0.f, 0.f), b = a;
+      if (row) {
+        a = *reinterpret_cast<const __nv_bfloat162*>(row + c);
+        b = *reinterpret_cast<const __nv_bfloat162*>(row + c + 8);
+      }
+      x[kk][0] = __low2float(a); x[kk][1] = __high2float(a); x[kk][2] = __low2float(b); x[kk][3] = __high2float(b);
+    }
+    auto norm = [&]() {
+      float ss = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ss = fmaf(x[kk][e], x[kk][e], ss);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+      const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const int c = kk * 16 + 2 * t;
+        if (weight != nullptr) {
+          x[kk][0] = x[kk][0] * inv * __ldg(weight + c);     x[kk][1] = x[kk][1] * inv * __ldg(weight + c + 1);
+          x[kk][2] = x[kk][2] * inv * __ldg(weight + c + 8); x[kk][3] = x[kk][3] * inv * __ldg(weight + c + 9);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) x[kk][e] = x[kk][e] * inv;
+        }
+      }
+    };
+    if (normed && !(mode & kNormAfterRotation)) norm();      // (every lane of the warp takes part in the exchange)
+    if (cs != nullptr && (mode & kPairsInterleaved)) {
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {                // the thread's neighbours (c, c + 1) and (c + 8, c + 9) are pairs
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int c = kk * 16 + 2 * t + 8 * h;
+          if (c + 1 < rd) {
+            const float2 w = __ldg(cs + c / 2);
+            const float a = x[kk][2 * h], b = x[kk][2 * h + 1];
+            x[kk][2 * h] = __fsub_rn(__fmul_rn(a, w.x), __fmul_rn(b, w.y));
+            x[kk][2 * h + 1] = __fadd_rn(__fmul_rn(a, w.y), __fmul_rn(b, w.x));
+          }
+        }
+      }
+    } else if (cs != nullptr) {
+#pragma unroll
+      for (int kk = 0; kk < D / 32; ++kk) {                // column i < D/2 pairs with i + D/2 = block kk + D/32
+        const int c = kk * 16 + 2 * t;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = c + (e & 1) + (e >> 1) * 8;
+          const float2 w = __ldg(cs + i);
+          const float a = x[kk][e], b = x[kk + D / 32][e];
+          // products and sums rounded separately, as the reference's scalar code does
+          x[kk][e] = __fsub_rn(__fmul_rn(a, w.x), __fmul_rn(b, w.y));
+          x[kk + D / 32][e] = __fadd_rn(__fmul_rn(a, w.y), __fmul_rn(b, w.x));
+        }
+      }
+    }
+    if (normed && (mode & kNormAfterRotation)) norm();
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      q[kk][r] = row ? pack_bf16(x[kk][0], x[kk][1]) : 0u;
+      q[kk][2 + r] = row ? pack_bf16(x[kk][2], x[kk][3]) : 0u;
+    }
+  }
+}
+
 // The step's own key and value (row `r` of a tile whose K slices start at `ks`, V slices at
 // `vs`): normed and rotated key, raw value, written over what TMA brought for that row, and
 // to the cache at `k_dst` / `v_dst` if those are not null.  Lane l holds elements
@@ -292,7 +382,99 @@ __device__ __forceinline__ void patch_new_key(uint32_t ks, uint32_t vs, int r, c
   __syncwarp();
 }
 
-template <int D, int kStages>
+// The same for the variants of the input stage, with the values kept for or mixed with the first
+// mixing layer's (`v_keep`: this (token, kv head)'s row of Params::v_first).
+template <int D>
+__device__ __forceinline__ void patch_new_key_variant(uint32_t ks, uint32_t vs, int r, const __nv_bfloat16* k_src,
+                                              const __nv_bfloat16* v_src, const float* k_weight, float eps, const float2* cs,
+                                              __nv_bfloat16* k_dst, __nv_bfloat16* v_dst, int lane, int mode, int rd,
+                                              int v_mode, __nv_bfloat16* v_keep, const float* v_lambda) {
+  constexpr int E = D / 64;
+  constexpr uint32_t kSlice = kKeys * 128;
+  float k[2][E], v[2][E];
+#pragma unroll
+  for (int h = 0; h < 2; ++h)
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      const int e = h * (D / 2) + E * lane + i;
+      k[h][i] = __bfloat162float(k_src[e]);
+      v[h][i] = __bfloat162float(v_src[e]);
+    }
+  const bool normed = k_weight != nullptr || (mode & kNormUnweighted);
+  auto norm = [&]() {
+    float ss = 0.f;
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int i = 0; i < E; ++i) ss = fmaf(k[h][i], k[h][i], ss);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int i = 0; i < E; ++i)
+        k[h][i] = k_weight != nullptr ? k[h][i] * inv * __ldg(k_weight + h * (D / 2) + E * lane + i) : k[h][i] * inv;
+  };
+  if (normed && !(mode & kNormAfterRotation)) norm();
+  if (cs != nullptr && (mode & kPairsInterleaved)) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if constexpr (E == 2) {                               // the lane's two elements of this half are a pair
+        const int e = h * (D / 2) + 2 * lane;
+        if (e + 1 < rd) {
+          const float2 w = __ldg(cs + e / 2);
+          const float a = k[h][0], b = k[h][1];
+          k[h][0] = __fsub_rn(__fmul_rn(a, w.x), __fmul_rn(b, w.y));
+          k[h][1] = __fadd_rn(__fmul_rn(a, w.y), __fmul_rn(b, w.x));
+        }
+      } else {                                              // one element a lane: the pair's other member is the neighbour lane's
+        const int e = h * (D / 2) + lane;
+        const float mine = k[h][0], other = __shfl_xor_sync(0xffffffffu, mine, 1);
+        if ((e | 1) < rd) {
+          const float2 w = __ldg(cs + e / 2);
+          k[h][0] = (lane & 1) ? __fadd_rn(__fmul_rn(other, w.y), __fmul_rn(mine, w.x))
+                               : __fsub_rn(__fmul_rn(mine, w.x), __fmul_rn(other, w.y));
+        }
+      }
+    }
+  } else if (cs != nullptr) {
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      const float2 w = __ldg(cs + E * lane + i);
+      const float a = k[0][i], b = k[1][i];
+      k[0][i] = __fsub_rn(__fmul_rn(a, w.x), __fmul_rn(b, w.y));
+      k[1][i] = __fadd_rn(__fmul_rn(a, w.y), __fmul_rn(b, w.x));
+    }
+  }
+  if (normed && (mode & kNormAfterRotation)) norm();
+  if (v_mode != 0) {
+    const float lam = v_mode == 2 ? __ldg(v_lambda) : 0.f;
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int i = 0; i < E; ++i) {
+        const int e = h * (D / 2) + E * lane + i;
+        if (v_mode == 2) v[h][i] = fmaf(lam, __bfloat162float(v_keep[e]), (1.0f - lam) * v[h][i]);
+        else if (v_dst != nullptr) v_keep[e] = __float2bfloat16_rn(v[h][i]);
+      }
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h)
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      const int e = h * (D / 2) + E * lane + i;
+      const __nv_bfloat16 kb = __float2bfloat16_rn(k[h][i]), vb = __float2bfloat16_rn(v[h][i]);
+      const uint32_t off = (uint32_t)(e >> 6) * kSlice + (uint32_t)r * 128u +
+                           (uint32_t)(((((e & 63) * 2) >> 4) ^ (r & 7)) << 4) + (uint32_t)(((e & 63) * 2) & 15);
+      asm volatile("st.shared.b16 [%0], %1;" ::"r"(ks + off), "h"(*reinterpret_cast<const unsigned short*>(&kb)) : "memory");
+      asm volatile("st.shared.b16 [%0], %1;" ::"r"(vs + off), "h"(*reinterpret_cast<const unsigned short*>(&vb)) : "memory");
+      if (k_dst != nullptr) { k_dst[e] = kb; v_dst[e] = vb; }
+    }
+  __syncwarp();
+}
+
+template <int D, int kStages, bool kVariant>
 __global__ void __launch_bounds__(kThreads)
 decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
               const __grid_constant__ CUtensorMap map_k_run, const __grid_constant__ CUtensorMap map_v_run, const Params p) {
@@ -433,8 +615,12 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
       for (int r = 0; r < 2; ++r) live[r] = rb + g + 8 * r < G;
       if (p.qkv != nullptr) {
         const __nv_bfloat16* base_q = p.qkv + (size_t)tok * p.qkv_stride + (size_t)(kvh * G + rb) * D;
-        load_q_fused<D>(q, live[0] ? base_q + (size_t)g * D : nullptr, live[1] ? base_q + (size_t)(g + 8) * D : nullptr,
-                        p.q_weight, p.eps, p.rope ? p.rope + (size_t)tok * (D / 2) : nullptr, lane);
+        if constexpr (kVariant)
+          load_q_variant<D>(q, live[0] ? base_q + (size_t)g * D : nullptr, live[1] ? base_q + (size_t)(g + 8) * D : nullptr,
+                            p.q_weight, p.eps, p.rope ? p.rope + (size_t)tok * (p.rotary_dim / 2) : nullptr, lane, p.mode, p.rotary_dim);
+        else
+          load_q_fused<D>(q, live[0] ? base_q + (size_t)g * D : nullptr, live[1] ? base_q + (size_t)(g + 8) * D : nullptr,
+                          p.q_weight, p.eps, p.rope ? p.rope + (size_t)tok * (D / 2) : nullptr, lane);
       } else {
         const __nv_bfloat16* row0 = live[0] ? p.q + (size_t)tok * p.q_stride + (size_t)(kvh * G + rb + g) * D : nullptr;
         const __nv_bfloat16* row1 = live[1] ? p.q + (size_t)tok * p.q_stride + (size_t)(kvh * G + rb + g + 8) * D : nullptr;
@@ -461,10 +647,17 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
           const int pg = blk < p.max_blocks ? __ldg(table + blk) : -1;
           const bool store = pass == 0 && pg >= 0 && pg < p.num_pages;     // never write outside the pool
           const size_t at = store ? (((size_t)pg * p.nkv + kvh) * p.page_size + (pos % p.page_size)) * D : 0;
-          patch_new_key<D>(base + s * kStage, base + s * kStage + kTensor, pos % kKeys,
-                           row + (size_t)(p.nq + kvh) * D, row + (size_t)(p.nq + p.nkv + kvh) * D, p.k_weight, p.eps,
-                           p.rope ? p.rope + (size_t)tok * (D / 2) : nullptr, store ? p.k_write + at : nullptr,
-                           store ? p.v_write + at : nullptr, lane);
+          if constexpr (kVariant)
+            patch_new_key_variant<D>(base + s * kStage, base + s * kStage + kTensor, pos % kKeys,
+                                     row + (size_t)(p.nq + kvh) * D, row + (size_t)(p.nq + p.nkv + kvh) * D, p.k_weight, p.eps,
+                                     p.rope ? p.rope + (size_t)tok * (p.rotary_dim / 2) : nullptr, store ? p.k_write + at : nullptr,
+                                     store ? p.v_write + at : nullptr, lane, p.mode, p.rotary_dim, p.v_mode,
+                                     p.v_first ? p.v_first + ((size_t)tok * p.nkv + kvh) * D : nullptr, p.v_lambda);
+          else
+            patch_new_key<D>(base + s * kStage, base + s * kStage + kTensor, pos % kKeys,
+                             row + (size_t)(p.nq + kvh) * D, row + (size_t)(p.nq + p.nkv + kvh) * D, p.k_weight, p.eps,
+                             p.rope ? p.rope + (size_t)tok * (D / 2) : nullptr, store ? p.k_write + at : nullptr,
+                             store ? p.v_write + at : nullptr, lane);
           // TMA will write this stage again later: order these ordinary stores before it
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         }
@@ -705,24 +898,24 @@ constexpr size_t ring_bytes() { return (size_t)STAGES * 2 * (D / 64) * kKeys * 1
 inline int rows_cap_of(int group, int split) { return (split > 1 && group <= 16) ? (group + split - 1) / split : 0; }
 inline size_t inbox_bytes(int d, int group, int split) { return (size_t)split * rows_cap_of(group, split) * (d + 4) * 4; }
 
-template <int D, int STAGES>
+template <int D, int STAGES, bool V = false>
 int configure() {
   static OncePerDevice once;
   if (once.first()) {
     constexpr size_t smem = ring_bytes<D, STAGES>() + (size_t)2 * kMaxSplit * (D + 4) * 4;   // the most a launch asks for
     static_assert(smem <= 227 * 1024, "tile ring does not fit shared memory");
-    cudaError_t e = cudaFuncSetAttribute(decode_kernel<D, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(decode_kernel<D, STAGES, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) once.forget();
     if (e != cudaSuccess) return fail("attention decode: cannot reserve %zu bytes of shared memory", smem);
-    cudaFuncSetAttribute(decode_kernel<D, STAGES>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    cudaFuncSetAttribute(decode_kernel<D, STAGES>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    cudaFuncSetAttribute(decode_kernel<D, STAGES, V>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(decode_kernel<D, STAGES, V>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
   }
   return 0;
 }
 
 // Clusters of `split` CTAs of this kernel, each with `extra` more bytes of shared memory, that
 // the device holds at a time (0 if it cannot tell or cannot run them).
-template <int D, int STAGES>
+template <int D, int STAGES, bool V = false>
 int active_clusters(int split, size_t extra) {
   static std::unordered_map<long long, int> cache;
   static std::mutex mu;
@@ -731,7 +924,7 @@ int active_clusters(int split, size_t extra) {
   std::lock_guard<std::mutex> g(mu);
   auto it = cache.find(key);
   if (it != cache.end()) return it->second;
-  if (configure<D, STAGES>()) return 0;
+  if (configure<D, STAGES, V>()) return 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(split, 64, 8);
   cfg.blockDim = dim3(kThreads);
@@ -741,16 +934,16 @@ int active_clusters(int split, size_t extra) {
   attr[0].val.clusterDim.x = (unsigned)split; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr; cfg.numAttrs = 1;
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, decode_kernel<D, STAGES>, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+  if (cudaOccupancyMaxActiveClusters(&n, decode_kernel<D, STAGES, V>, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
   if (n < 0) n = 0;
   cache.emplace(key, n);
   return n;
 }
 
-template <int D, int STAGES>
+template <int D, int STAGES, bool V = false>
 int launch(const CUtensorMap (&m)[4], const Params& p, size_t extra, cudaStream_t stream) {
-  if (configure<D, STAGES>()) return -1;
-  ilb::launch_cluster(decode_kernel<D, STAGES>, dim3(p.split, p.nkv, p.n_seqs * p.chunks), dim3(kThreads), ring_bytes<D, STAGES>() + extra, stream,
+  if (configure<D, STAGES, V>()) return -1;
+  ilb::launch_cluster(decode_kernel<D, STAGES, V>, dim3(p.split, p.nkv, p.n_seqs * p.chunks), dim3(kThreads), ring_bytes<D, STAGES>() + extra, stream,
                       p.split, m[0], m[1], m[2], m[3], p);
   return check_launch("attention decode");
 }
@@ -762,18 +955,18 @@ constexpr int kMaxChunks = 8;
 // `long_context`: the step's longest sequence is long enough for several clusters per
 // (sequence, kv head) to pay; the launch is then shaped for the most CTAs at work, not for the
 // widest cluster.
-template <int D>
+template <int D, bool V = false>
 void plan_for(int n_seqs, int nq, int nkv, int long_context, int& split, int& stages, int& chunks) {
   const long long pairs = (long long)n_seqs * nkv;
   const int group = nq / nkv;
   split = kMaxSplit;
-  while (split > 1 && active_clusters<D, 3>(split, inbox_bytes(D, group, split)) < pairs) split /= 2;
+  while (split > 1 && active_clusters<D, 3, V>(split, inbox_bytes(D, group, split)) < pairs) split /= 2;
   chunks = 1;
   if (long_context && split > 1 && group <= 16) {
     long long best = 0;
     int best_split = split;
     for (int s = split; s >= 2; s /= 2) {
-      long long c = active_clusters<D, 3>(s, inbox_bytes(D, group, s)) / pairs;
+      long long c = active_clusters<D, 3, V>(s, inbox_bytes(D, group, s)) / pairs;
       c = c > kMaxChunks ? kMaxChunks : c;
       if (c * s > best) { best = c * s; best_split = s; chunks = (int)c; }
     }
@@ -781,24 +974,24 @@ void plan_for(int n_seqs, int nq, int nkv, int long_context, int& split, int& st
   }
   const size_t extra = inbox_bytes(D, group, split);
   const long long clusters = pairs * chunks;
-  stages = active_clusters<D, 12>(split, extra) >= clusters ? 12 : active_clusters<D, 6>(split, extra) >= clusters ? 6 : 3;
+  stages = active_clusters<D, 12, V>(split, extra) >= clusters ? 12 : active_clusters<D, 6, V>(split, extra) >= clusters ? 6 : 3;
 }
 
-template <int D>
+template <int D, bool V = false>
 int launch_for(const CUtensorMap (&m)[4], Params& p, int long_context, long long scratch_floats, long long n_counters, cudaStream_t stream) {
   int stages = 3;
-  plan_for<D>(p.n_seqs, p.nq, p.nkv, long_context, p.split, stages, p.chunks);
+  plan_for<D, V>(p.n_seqs, p.nq, p.nkv, long_context, p.split, stages, p.chunks);
   const int group = p.nq / p.nkv;
   if (p.chunks > 1) {
     const long long need_f = (long long)p.n_seqs * p.nkv * p.chunks * 16 * (D + 2), need_c = (long long)p.n_seqs * p.nkv * 16;
     if (p.scratch == nullptr || p.counters == nullptr || need_f > scratch_floats || need_c > n_counters)
-      plan_for<D>(p.n_seqs, p.nq, p.nkv, 0, p.split, stages, p.chunks);       // no room for the records: one cluster each
+      plan_for<D, V>(p.n_seqs, p.nq, p.nkv, 0, p.split, stages, p.chunks);       // no room for the records: one cluster each
   }
   p.rows_cap = rows_cap_of(group, p.split);
   const size_t extra = inbox_bytes(D, group, p.split);
-  if (stages == 12) return launch<D, 12>(m, p, extra, stream);
-  if (stages == 6) return launch<D, 6>(m, p, extra, stream);
-  return launch<D, 3>(m, p, extra, stream);
+  if (stages == 12) return launch<D, 12, V>(m, p, extra, stream);
+  if (stages == 6) return launch<D, 6, V>(m, p, extra, stream);
+  return launch<D, 3, V>(m, p, extra, stream);
 }
 
 }  // namespace
@@ -827,8 +1020,10 @@ ILB_EXPORT long long ilb_attention_decode_scratch_floats(int n_seqs, int nkv, in
 ILB_EXPORT long long ilb_attention_decode_counters(int n_seqs, int nkv) { return (long long)n_seqs * nkv * 16; }
 
 namespace {
+struct InputStage { int mode = 0, rotary_dim = 0, v_mode = 0; void* v_first = nullptr; const float* v_lambda = nullptr; };
+
 int decode_common(const void* q, const void* qkv, int qkv_stride, const float* q_weight, const float* k_weight, float eps,
-                  const float* rope, int write_kv, void* out, const void* k_cache, const void* v_cache, const int* positions,
+                  const float* rope, const InputStage& in, int write_kv, void* out, const void* k_cache, const void* v_cache, const int* positions,
                   const int* cu_q, const int* block_table, int max_blocks, int page_size, int num_pages, int window,
                   float scale, int n_seqs, int nq, int nkv, int d, int q_stride, int out_stride, int long_context,
                   float* scratch, long long scratch_floats, int* counters, long long n_counters, int* error_flag, cudaStream_t stream) {
@@ -856,9 +1051,14 @@ int decode_common(const void* q, const void* qkv, int qkv_stride, const float* q
   p.split = 1; p.scale_log2 = scale * kLog2e;
   p.qkv = (const __nv_bfloat16*)qkv; p.qkv_stride = qkv_stride; p.q_weight = q_weight; p.k_weight = k_weight; p.eps = eps;
   p.rope = (const float2*)rope;
+  p.mode = in.mode; p.rotary_dim = in.rotary_dim > 0 ? in.rotary_dim : d; p.v_mode = in.v_mode;
+  p.v_first = (__nv_bfloat16*)in.v_first; p.v_lambda = in.v_lambda;
   p.k_write = (qkv != nullptr && write_kv) ? (__nv_bfloat16*)const_cast<void*>(k_cache) : nullptr;
   p.v_write = (qkv != nullptr && write_kv) ? (__nv_bfloat16*)const_cast<void*>(v_cache) : nullptr;
   p.chunks = 1; p.scratch = scratch; p.counters = counters;
+  if (p.mode != 0 || p.v_mode != 0)        // the input stage's variants are a kernel of their own: the stock one stays as it was
+    return d == 64 ? launch_for<64, true>(m, p, long_context, scratch_floats, n_counters, stream)
+                   : launch_for<128, true>(m, p, long_context, scratch_floats, n_counters, stream);
   return d == 64 ? launch_for<64>(m, p, long_context, scratch_floats, n_counters, stream)
                  : launch_for<128>(m, p, long_context, scratch_floats, n_counters, stream);
 }
@@ -870,7 +1070,7 @@ ILB_EXPORT int ilb_attention_decode_tma(const void* q, void* out, const void* k_
                                         int n_seqs, int nq, int nkv, int d, int q_stride, int out_stride,
                                         int long_context, float* scratch, long long scratch_floats, int* counters, long long n_counters,
                                         int* error_flag, cudaStream_t stream) {
-  return decode_common(q, nullptr, 0, nullptr, nullptr, 1.f, nullptr, 0, out, k_cache, v_cache, positions, cu_q, block_table,
+  return decode_common(q, nullptr, 0, nullptr, nullptr, 1.f, nullptr, InputStage{}, 0, out, k_cache, v_cache, positions, cu_q, block_table,
                        max_blocks, page_size, num_pages, window, scale, n_seqs, nq, nkv, d, q_stride, out_stride, long_context,
                        scratch, scratch_floats, counters, n_counters, error_flag, stream);
 }
@@ -879,15 +1079,24 @@ ILB_EXPORT int ilb_attention_decode_tma(const void* q, void* out, const void* k_
 // [tokens, (nq + 2 nkv) d]: per-head RMSNorm (q_weight / k_weight [d], or null), rotation over
 // the whole head (rope [tokens, d/2, 2] cos/sin, or null), and, if write_kv, the new key and
 // value stored to the cache.  What qk_norm_rope.cu and this kernel do in two launches.
+// `mode`, `rotary_dim` and the value mixing (`v_mode`, `v_first`, `v_lambda`) are described at Params.
 ILB_EXPORT int ilb_attention_decode_fused(const void* qkv, int qkv_stride, const float* q_weight, const float* k_weight,
-                                          float eps, const float* rope, int write_kv, void* out, void* k_cache,
+                                          float eps, const float* rope, int mode, int rotary_dim, int v_mode, void* v_first,
+                                          const float* v_lambda, int write_kv, void* out, void* k_cache,
                                           void* v_cache, const int* positions, const int* cu_q, const int* block_table,
                                           int max_blocks, int page_size, int num_pages, int window, float scale,
                                           int n_seqs, int nq, int nkv, int d, int out_stride, int long_context,
                                           float* scratch, long long scratch_floats, int* counters, long long n_counters, int* error_flag,
                                           cudaStream_t stream) {
   ILB_REQUIRE(qkv != nullptr, "attention decode: no projection output");
-  return decode_common(nullptr, qkv, qkv_stride, q_weight, k_weight, eps, rope, write_kv, out, k_cache, v_cache, positions,
+  ILB_REQUIRE(mode >= 0 && mode < 8 && v_mode >= 0 && v_mode <= 2, "attention decode: unknown input stage %d / %d", mode, v_mode);
+  ILB_REQUIRE(rope == nullptr || ((mode & 1) ? (rotary_dim > 0 && rotary_dim % 2 == 0 && rotary_dim <= d) : rotary_dim == d),
+              "attention decode: a rotation over %d of %d elements is not built for this pairing", rotary_dim, d);
+  ILB_REQUIRE(v_mode == 0 || (v_first != nullptr && write_kv), "attention decode: value mixing needs the first values and a cache write");
+  ILB_REQUIRE(v_mode != 2 || v_lambda != nullptr, "attention decode: value mixing needs its coefficient");
+  InputStage in;
+  in.mode = mode; in.rotary_dim = rotary_dim; in.v_mode = v_mode; in.v_first = v_first; in.v_lambda = v_lambda;
+  return decode_common(nullptr, qkv, qkv_stride, q_weight, k_weight, eps, rope, in, write_kv, out, k_cache, v_cache, positions,
                        cu_q, block_table, max_blocks, page_size, num_pages, window, scale, n_seqs, nq, nkv, d, 0, out_stride,
                        long_context, scratch, scratch_floats, counters, n_counters, error_flag, stream);
 }

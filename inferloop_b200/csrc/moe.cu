@@ -31,10 +31,10 @@ __device__ __forceinline__ float sigmoid_stable(float x) {
 }
 
 // Router logits: out[t, e] = x[t, :] . w[e, :] in 32-bit for a few rows of w (the experts, and a
-// gate's row riding along).  A warp owns one token and walks kLogitRows rows of w: lanes take
-// consecutive pieces of eight features; a piece is one chain of fused multiply-adds from zero,
-// the pieces of a lane are added with the rounding error of every addition carried along in a
-// second word (two-sum), and the lanes meet in a butterfly sum.  The order of a logit's sum
+// gate's row riding along).  A block of four warps owns one token and kLogitRows rows of w:
+// threads take consecutive pieces of eight features; a piece is one chain of fused multiply-adds
+// from zero, the pieces of a thread are added with the rounding error of every addition carried
+// along in a second word (two-sum), the lanes meet in a butterfly sum and the warps in a fixed order.  The order of a logit's sum
 // depends on the width alone, and its error stays near that of eight terms, not of the width.
 constexpr int kLogitRows = 4;
 
@@ -60,9 +60,9 @@ moe_logits_kernel(const T* __restrict__ x, const T* __restrict__ w, float* __res
                   int vec) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
+  __shared__ float part_sum[4][kLogitRows];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * 4 + warp;
-  if (t >= n_tokens) return;
+  const int t = blockIdx.x;
   const T* xr = x + (size_t)t * width;
   const int e0 = blockIdx.y * kLogitRows;
   float acc[kLogitRows], lost[kLogitRows];
@@ -75,7 +75,7 @@ moe_logits_kernel(const T* __restrict__ x, const T* __restrict__ w, float* __res
     acc[r] = sum;
   };
   if (vec) {
-    for (int i = lane * 8; i < width; i += 256) {
+    for (int i = threadIdx.x * 8; i < width; i += 1024) {
       float xv[8];
       Piece8<T>::load(xr + i, xv);
 #pragma unroll
@@ -90,7 +90,7 @@ moe_logits_kernel(const T* __restrict__ x, const T* __restrict__ w, float* __res
       }
     }
   } else {
-    for (int i = lane; i < width; i += 32) {
+    for (int i = threadIdx.x; i < width; i += 128) {
       const float xv = to_float(xr[i]);
 #pragma unroll
       for (int r = 0; r < kLogitRows; ++r)
@@ -100,7 +100,12 @@ moe_logits_kernel(const T* __restrict__ x, const T* __restrict__ w, float* __res
 #pragma unroll
   for (int r = 0; r < kLogitRows; ++r) {
     const float v = warp_sum(__fadd_rn(acc[r], lost[r]));
-    if (lane == 0 && e0 + r < rows) out[(size_t)t * rows + e0 + r] = v;
+    if (lane == 0) part_sum[warp][r] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x < kLogitRows && e0 + threadIdx.x < rows) {
+    const int r = threadIdx.x;
+    out[(size_t)t * rows + e0 + r] = (part_sum[0][r] + part_sum[1][r]) + (part_sum[2][r] + part_sum[3][r]);
   }
 }
 
@@ -110,7 +115,7 @@ ILB_EXPORT int ilb_moe_logits(const void* x, const void* w, int dtype, float* ou
   ILB_REQUIRE(n_tokens >= 0 && rows > 0 && width > 0, "moe_logits: bad sizes");
   ILB_REQUIRE((rows + kLogitRows - 1) / kLogitRows <= 65535, "moe_logits: too many rows");
   if (n_tokens == 0) return 0;
-  const dim3 grid((n_tokens + 3) / 4, (rows + kLogitRows - 1) / kLogitRows);
+  const dim3 grid(n_tokens, (rows + kLogitRows - 1) / kLogitRows);
   const int vec = (width % 8 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0)) ? 1 : 0;
   if (dtype == kF32)
     ilb::launch(moe_logits_kernel<float>, grid, dim3(128), 0, stream, (const float*)x, (const float*)w, out, n_tokens, rows, width, vec);
@@ -272,11 +277,12 @@ moe_gather_kernel(const T* __restrict__ x, const float* __restrict__ weight, con
   if (row < 0) return;
   T* o = out + (size_t)row * width;
   const T* src = x + (size_t)(p / top) * width;
+  const int step = blockDim.x * gridDim.y, first = blockIdx.y * blockDim.x + threadIdx.x;    // the row is dealt over gridDim.y blocks
   if (weight == nullptr) {
-    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = src[i];
+    for (int i = first; i < width; i += step) o[i] = src[i];
   } else {
     const float w = weight[p];
-    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_float<T>(w * to_float(src[i]));
+    for (int i = first; i < width; i += step) o[i] = from_float<T>(w * to_float(src[i]));
   }
 }
 
@@ -286,10 +292,11 @@ ILB_EXPORT int ilb_moe_gather(const void* x, int dtype, const float* weight, con
                               void* out, cudaStream_t stream) {
   ILB_REQUIRE(n_pairs >= 0 && top > 0 && width > 0, "moe_gather: bad sizes");
   if (n_pairs == 0) return 0;
+  const int ny = n_pairs >= 512 ? 1 : (width + 511) / 512 < 16 ? (width + 511) / 512 : 16;     // few pairs: more blocks per row
   if (dtype == kF32)
-    ilb::launch(moe_gather_kernel<float>, dim3(n_pairs), dim3(128), 0, stream, (const float*)x, weight, pos, top, width, (float*)out);
+    ilb::launch(moe_gather_kernel<float>, dim3(n_pairs, ny), dim3(128), 0, stream, (const float*)x, weight, pos, top, width, (float*)out);
   else if (dtype == kBF16)
-    ilb::launch(moe_gather_kernel<__nv_bfloat16>, dim3(n_pairs), dim3(128), 0, stream, (const __nv_bfloat16*)x, weight, pos, top,
+    ilb::launch(moe_gather_kernel<__nv_bfloat16>, dim3(n_pairs, ny), dim3(128), 0, stream, (const __nv_bfloat16*)x, weight, pos, top,
                 width, (__nv_bfloat16*)out);
   else
     return fail("moe_gather: unknown dtype %d", dtype);
@@ -312,7 +319,7 @@ moe_combine_kernel(const float* __restrict__ routed, const int* __restrict__ pos
   __syncthreads();
   float gate = 1.0f;
   if (shared != nullptr && gate_logit != nullptr) gate = sigmoid_stable(gate_logit[(size_t)t * gate_ld]);
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < width; i += blockDim.x * gridDim.y) {
     float v = 0.f;
     for (int j = 0; j < top; ++j)
       if (rows[j] >= 0) v = fmaf(ws[j], routed[(size_t)rows[j] * width + i], v);
@@ -328,7 +335,8 @@ ILB_EXPORT int ilb_moe_combine(const float* routed, const int* pos, const float*
                                const float* gate_logit, int gate_ld, int n_tokens, int width, float* y, cudaStream_t stream) {
   ILB_REQUIRE(n_tokens >= 0 && top > 0 && top <= kMaxTop && width > 0, "moe_combine: bad sizes");
   if (n_tokens == 0) return 0;
-  ilb::launch(moe_combine_kernel, dim3(n_tokens), dim3(128), 0, stream, routed, pos, weight, top, shared, gate_logit, gate_ld, width, y);
+  const int ny = n_tokens >= 512 ? 1 : (width + 255) / 256 < 32 ? (width + 255) / 256 : 32;    // few tokens: more blocks per row
+  ilb::launch(moe_combine_kernel, dim3(n_tokens, ny), dim3(128), 0, stream, routed, pos, weight, top, shared, gate_logit, gate_ld, width, y);
   return check_launch("moe_combine");
 }
 

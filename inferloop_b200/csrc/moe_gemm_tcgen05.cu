@@ -8,11 +8,11 @@
 // One CTA computes one tile: D accumulates in tensor memory over K; warp 0 (one lane) streams
 // the operands by TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) through a ring of
 // three stages, warp 1 (one lane) issues tcgen05.mma and commits, warps 2-5 read the
-// accumulators with tcgen05.ld and write the rows out.  Two tile shapes: 128 rows x 128 weight
+// accumulators with tcgen05.ld and write the rows out.  Tile shapes: 128 rows x 128 weight
 // rows, two CTAs to an SM so that one tile's write-out runs under the other's products (few
-// rows per expert: the launch streams the chosen experts' weights); and 256 rows x 256 weight
-// rows (two 128-row accumulators that share every weight block, all 512 columns of tensor memory),
-// which halves the operand bytes per flop when experts have hundreds of rows.  The weight tile of group
+// rows per expert: the launch streams the chosen experts' weights); 128 x 256 with a ring of four
+// stages; and 256 x 256 (two 128-row accumulators that share every weight block, all 512 columns
+// of tensor memory): wider tiles need fewer operand bytes per flop.  The weight tile of group
 // g starts at row g * N + n0 of the stacked matrix; columns past N are not written, so a tile
 // that reaches into the next group's rows (or past the end, where TMA fills zeros) is harmless.
 // With the SwiGLU epilogue W holds blocks of 64 gate rows followed by their 64 up rows, a tile is
@@ -31,11 +31,10 @@ namespace {
 
 constexpr int kBlockK = 64;             // bf16 elements per K block = one 128-byte swizzle row
 constexpr int kRows = 128;              // rows of one accumulator = MMA M
-constexpr int kStages = 3;
 constexpr uint32_t kBytesA = kRows * kBlockK * 2;
 // MS row blocks of 128 and BN weight rows per tile
 template <int MS, int BN> __host__ __device__ constexpr uint32_t stage_bytes() { return MS * kBytesA + BN * kBlockK * 2; }
-template <int MS, int BN> constexpr size_t smem_bytes() { return (size_t)kStages * stage_bytes<MS, BN>() + 1024 + (2 * kStages + 4) * 8; }
+template <int MS, int BN, int kStages> constexpr size_t smem_bytes() { return (size_t)kStages * stage_bytes<MS, BN>() + 1024 + (2 * kStages + 4) * 8; }
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
@@ -81,8 +80,8 @@ __device__ __forceinline__ void store32(const Params& p, size_t out_row, int c, 
   }
 }
 
-template <int MS, int BN>
-__global__ void __launch_bounds__(192, MS == 1 ? 2 : 1)
+template <int MS, int BN, int kStages>
+__global__ void __launch_bounds__(192, (MS == 1 && BN == 128) ? 2 : 1)
 moe_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const Params p) {
   constexpr uint32_t kStageBytes = stage_bytes<MS, BN>();
   constexpr uint32_t kTmemCols = MS * BN;          // 128 or 512: a power of two
@@ -241,19 +240,19 @@ int make_map(CUtensorMap* out, const void* ptr, long long rows, int cols, int ld
 
 }  // namespace
 
-template <int MS, int BN>
+template <int MS, int BN, int kStages>
 static int launch_tiles(const void* A, const void* W, const Params& p, int rows, int groups, int lda, cudaStream_t stream) {
   static OncePerDevice once;
-  constexpr size_t smem = smem_bytes<MS, BN>();
+  constexpr size_t smem = smem_bytes<MS, BN, kStages>();
   if (once.first() &&
-      cudaFuncSetAttribute(moe_gemm_kernel<MS, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+      cudaFuncSetAttribute(moe_gemm_kernel<MS, BN, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
     once.forget();
     return fail("moe_gemm: cannot reserve %zu bytes of shared memory", smem);
   }
   CUtensorMap ma, mw;
   if (make_map(&ma, A, rows, p.K, lda, kRows)) return -1;
   if (make_map(&mw, W, (long long)groups * p.N, p.K, p.K, BN)) return -1;
-  ilb::launch(moe_gemm_kernel<MS, BN>, dim3((p.N + BN - 1) / BN, rows / (MS * kRows)), dim3(192), smem, stream, ma, mw, p);
+  ilb::launch(moe_gemm_kernel<MS, BN, kStages>, dim3((p.N + BN - 1) / BN, rows / (MS * kRows)), dim3(192), smem, stream, ma, mw, p);
   return check_launch("moe_gemm_tc");
 }
 
@@ -264,11 +263,13 @@ ILB_EXPORT int ilb_moe_gemm_tc_supported(int N, int K, int lda, int swiglu) {
 
 // A: [rows, K] bf16 (leading dimension lda); W: [groups, N, K] bf16, contiguous; out: [rows, N]
 // (with swiglu: [rows, N / 2]) bf16 or f32 with leading dimension ldo; block_group: [rows / block_rows],
-// block_rows = 128 or 256 (the tile is then 128 x 128 or 256 x 256).
+// block_rows = 128 or 256; tile_n = 128 or 256 weight rows per tile (256 rows take 256).
 ILB_EXPORT int ilb_moe_gemm_tc(const void* A, const void* W, void* out, int out_f32, int rows, int groups, int N, int K, int lda,
-                               int ldo, int swiglu, const int* block_group, int block_rows, int* error_flag, cudaStream_t stream) {
+                               int ldo, int swiglu, const int* block_group, int block_rows, int tile_n, int* error_flag,
+                               cudaStream_t stream) {
   ILB_REQUIRE(rows >= 0 && groups > 0 && N > 0 && K > 0, "moe_gemm: bad sizes rows=%d groups=%d N=%d K=%d", rows, groups, N, K);
   ILB_REQUIRE(block_rows == 128 || block_rows == 256, "moe_gemm: blocks of 128 or 256 rows, not %d", block_rows);
+  ILB_REQUIRE(tile_n == 256 || (tile_n == 128 && block_rows == 128), "moe_gemm: tiles of %d x %d are not built", block_rows, tile_n);
   ILB_REQUIRE(rows % block_rows == 0 && rows / block_rows <= 65535, "moe_gemm: rows must come in blocks of %d (at most 65535 blocks)", block_rows);
   ILB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && lda >= K && ((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0),
               "moe_gemm: operands must have rows of whole 16 bytes on 16-byte boundaries");
@@ -281,8 +282,9 @@ ILB_EXPORT int ilb_moe_gemm_tc(const void* A, const void* W, void* out, int out_
   p.out = out; p.block_group = block_group; p.error_flag = error_flag;
   p.N = N; p.K = K; p.ldo = ldo; p.k_blocks = (K + kBlockK - 1) / kBlockK;
   p.swiglu = swiglu ? 1 : 0; p.out_f32 = out_f32 ? 1 : 0;
-  if (block_rows == 256) return launch_tiles<2, 256>(A, W, p, rows, groups, lda, stream);
-  return launch_tiles<1, 128>(A, W, p, rows, groups, lda, stream);
+  if (block_rows == 256) return launch_tiles<2, 256, 3>(A, W, p, rows, groups, lda, stream);
+  if (tile_n == 256) return launch_tiles<1, 256, 4>(A, W, p, rows, groups, lda, stream);
+  return launch_tiles<1, 128, 3>(A, W, p, rows, groups, lda, stream);
 }
 
 ILB_DEFINE_LAST_ERROR()

@@ -251,8 +251,12 @@ def moe_gemm_tc_eligible(a: torch.Tensor, w: torch.Tensor, swiglu: bool = False)
             and (not swiglu or w.shape[1] % 128 == 0))
 
 
+MOE_WIDE_BLOCKS = True     # blocks of 256 rows (256 x 256 tiles) once an expert gets a thousand rows on average
+MOE_TILE_N = 0             # tests and measurements force 128 or 256 weight rows per tile of 128 rows; 0: the default choice
+
+
 def moe_gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, block_group: torch.Tensor, swiglu: bool = False,
-                block_rows: int = GROUP_ROWS_TC) -> None:
+                block_rows: int = GROUP_ROWS_TC, tile_n: int = 0) -> None:
     """out[rows of block b] = a[rows of block b] @ w[block_group[b]].T on tcgen05 tensor cores for
     blocks of 128 or 256 rows (moe_gemm_tcgen05.cu); with `swiglu`, w holds blocks of 64 gate rows
     followed by their 64 up rows and out is [rows, N / 2] = silu(gate) * up."""
@@ -264,10 +268,15 @@ def moe_gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, block_group
     N = w.shape[1]
     if tuple(out.shape) != (M, N // 2 if swiglu else N) or out.dtype not in (torch.float32, torch.bfloat16):
         raise KernelError(f"moe_gemm_tc: output {tuple(out.shape)} {out.dtype} does not fit")
+    if block_rows == GROUP_ROWS_TC_WIDE:
+        tile_n = 256
+    elif not tile_n:
+        # a tile of 256 weight rows halves the bytes of the rows' operand per flop; it pays once the rows are many
+        tile_n = MOE_TILE_N or (256 if M >= 2048 and N >= 512 else 128)
     st = _tc_state(a.device)
     _call("moe_gemm_tcgen05", "ilb_moe_gemm_tc", _ptr(a), _ptr(w), _ptr(out), _i(1 if out.dtype == torch.float32 else 0), _i(M),
           _i(w.shape[0]), _i(N), _i(K), _i(a.stride(0)), _i(out.stride(0)), _i(1 if swiglu else 0), _ptr(block_group),
-          _i(block_rows), _ptr(st.error), _stream(out))
+          _i(block_rows), _i(tile_n), _ptr(st.error), _stream(out))
 
 
 def gemm_simt_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, block_group: torch.Tensor) -> None:
@@ -675,18 +684,28 @@ def attention_decode_tma(q, out, k_cache, v_cache, positions, cu_q, block_table,
 
 
 def attention_decode_fused_supported(dtype: torch.dtype, cache_dtype: torch.dtype, nq: int, nkv: int, d: int,
-                                     page_size: int, rotary_dim: int, has_rope: bool) -> bool:
+                                     page_size: int, rotary_dim: int, has_rope: bool, interleaved: bool = False) -> bool:
     """Whether a decode-only step can take q/k/v straight from the fused projection output:
-    the TMA decode kernel's geometry, bfloat16 throughout, rotation over the whole head."""
+    the TMA decode kernel's geometry, bfloat16 throughout, rotation over the whole head (pairs
+    of neighbours: over any even part of it)."""
     return (DECODE_CLUSTER_ENABLED and DECODE_FUSED_ENABLED and FLASH_ENABLED and dtype == torch.bfloat16
             and cache_dtype == torch.bfloat16 and attention_decode_tma_supported(nq, nkv, d, page_size)
-            and (not has_rope or rotary_dim == d))
+            and (not has_rope or rotary_dim == d or (interleaved and 0 < rotary_dim <= d and rotary_dim % 2 == 0)))
 
 
 def attention_decode_fused(qkv, out, q_weight, k_weight, eps, rope_table, k_cache, v_cache, write_kv, positions, cu_q,
-                           block_table, window, scale, n_seqs, nq, nkv, d, long_context: bool = False) -> None:
+                           block_table, window, scale, n_seqs, nq, nkv, d, long_context: bool = False, mode: int = 0,
+                           rotary_dim: Optional[int] = None, v_first: Optional[torch.Tensor] = None,
+                           v_lambda: Optional[torch.Tensor] = None, v_keep: bool = False) -> None:
     """Decode attention with the per-head q/k norm, the rotation and the cache write of the
-    step's own key and value inside the attention kernel (one launch instead of two)."""
+    step's own key and value inside the attention kernel (one launch instead of two).  `mode`,
+    `rotary_dim`, `v_first`, `v_lambda` and `v_keep` as in `qk_norm_rope_cache`."""
+    v_mode = 0
+    if v_keep or v_lambda is not None:
+        _need(v_first, "first values", torch.bfloat16); _need(v_lambda, "value mixing coefficient", torch.float32)
+        if v_first is None or tuple(v_first.shape) != (qkv.shape[0], nkv * d) or (v_keep and v_lambda is not None):
+            raise KernelError("value mixing needs first values [tokens, nkv * d], and either keeps or mixes them")
+        v_mode = 1 if v_keep else 2
     for t, w in ((qkv, "qkv"), (out, "out"), (k_cache, "k cache"), (v_cache, "v cache")):
         _need(t, "attention " + w, torch.bfloat16)
     for t, w in ((q_weight, "q norm weight"), (k_weight, "k norm weight"), (rope_table, "rope table")):
@@ -695,8 +714,9 @@ def attention_decode_fused(qkv, out, q_weight, k_weight, eps, rope_table, k_cach
     num_pages, _, page_size, _ = k_cache.shape
     st = _tc_state(qkv.device)
     _call("attention_decode", "ilb_attention_decode_fused", _ptr(qkv), _i(qkv.shape[1]), _ptr(q_weight), _ptr(k_weight),
-          _f(eps if eps and eps > 0 else 1e-6), _ptr(rope_table), _i(1 if write_kv else 0), _ptr(out), _ptr(k_cache),
-          _ptr(v_cache), _ptr(positions),
+          _f(eps if eps and eps > 0 else 1e-6), _ptr(rope_table), _i(mode), _i(d if rotary_dim is None else rotary_dim), _i(v_mode),
+          _ptr(v_first if v_mode else None), _ptr(v_lambda if v_mode == 2 else None), _i(1 if write_kv else 0), _ptr(out),
+          _ptr(k_cache), _ptr(v_cache), _ptr(positions),
           _ptr(cu_q), _ptr(block_table), _i(block_table.shape[1]), _i(page_size), _i(num_pages), _i(window or 0),
           _f(scale), _i(n_seqs), _i(nq), _i(nkv), _i(d), _i(out.shape[1]), _i(1 if long_context else 0), _ptr(st.attn_scratch),
           ctypes.c_longlong(st.attn_scratch.numel()), _ptr(st.attn_counters), ctypes.c_longlong(st.attn_counters.numel()),

@@ -145,9 +145,10 @@ class GQAttention(Mixer):
         if self.value_mix is not None:
             # the step's tokens' values of the first layer that mixes: kept by it, read by the later ones
             v_first = ws.buffer(f"attn.v_first/{self.nkv}x{self.dv}", (T, self.nkv * self.dv), dt)
-        stock = self.mode == 0 and self.dv == self.d and self.value_mix is None
-        if (stock and step.decode_only and cache.k is not None and ops.attention_decode_fused_supported(
-                dt, cache.k.dtype, self.nq, self.nkv, self.d, cache.page_size, self.rotary_dim, rope is not None)):
+        if (self.dv == self.d and step.decode_only and cache.k is not None and (cache.writable or self.value_mix is None)
+                and ops.attention_decode_fused_supported(
+                    dt, cache.k.dtype, self.nq, self.nkv, self.d, cache.page_size, self.rotary_dim, rope is not None,
+                    interleaved=bool(self.mode & ops.ROPE_INTERLEAVED))):
             # one token per sequence: norm, rotation and the cache write of the new key and
             # value happen inside the attention kernel
             o = ws.buffer("attn.o", (T, self.nq * self.d), dt)
@@ -155,7 +156,10 @@ class GQAttention(Mixer):
             ops.attention_decode_fused(qkv, o, self.q_norm, self.k_norm, self.qk_norm_eps, rope, cache.k, cache.v,
                                        cache.writable, step.positions, step.cu_q, table, self.window or 0, self.scale,
                                        step.n_seqs, self.nq, self.nkv, self.d,
-                                       long_context=step.max_kv_len >= ops.DECODE_LONG_CONTEXT)
+                                       long_context=step.max_kv_len >= ops.DECODE_LONG_CONTEXT, mode=self.mode,
+                                       rotary_dim=self.rotary_dim or None, v_first=v_first,
+                                       v_lambda=self.v_lambda if self.value_mix == "mixed" else None,
+                                       v_keep=self.value_mix == "first")
             ops.scope("attention.o_projection")
             linear(o, self.w_o, residual, self.b_o, accumulate=True)
             return

@@ -380,10 +380,10 @@ def test_router_logits_are_32_bit_sums(dtype, T, rows, width):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("block", [16, 128, 256])
+@pytest.mark.parametrize("block,tile_n", [(16, 0), (128, 128), (128, 256), (256, 256)])
 @pytest.mark.parametrize("T,experts,top,H,I", [(1, 4, 2, 64, 64), (9, 5, 2, 96, 128), (300, 8, 1, 256, 64), (77, 3, 3, 128, 192),
                                                (700, 2, 2, 320, 384)])
-def test_sorted_rows_grouped_products_and_the_sum(dtype, block, T, experts, top, H, I):
+def test_sorted_rows_grouped_products_and_the_sum(dtype, block, tile_n, T, experts, top, H, I):
     """plan -> gather -> grouped product (exact in blocks of 16; on tensor cores in blocks of 128 and 256,
     with and without the SwiGLU epilogue) -> combine, with weights on the input and on the output,
     against per-token products."""
@@ -412,7 +412,7 @@ def test_sorted_rows_grouped_products_and_the_sum(dtype, block, T, experts, top,
         if block == 16:
             ops.gemm_simt_grouped(a, w1.to(DEV), out, block_expert)
         else:
-            ops.moe_gemm_tc(a, w1.to(DEV), out, block_expert, block_rows=block)
+            ops.moe_gemm_tc(a, w1.to(DEV), out, block_expert, block_rows=block, tile_n=tile_n)
         y = torch.zeros(T, I, dtype=torch.float32, device=DEV)
         shared = torch.randn(T, I, generator=g)
         gate = torch.randn(T, 3, generator=g)
@@ -430,7 +430,7 @@ def test_sorted_rows_grouped_products_and_the_sum(dtype, block, T, experts, top,
         wg, wu = (torch.randn(experts, I, H, generator=g) * 0.2).to(dtype), (torch.randn(experts, I, H, generator=g) * 0.2).to(dtype)
         inter = torch.stack([wg.view(experts, I // 64, 64, H), wu.view(experts, I // 64, 64, H)], dim=2).reshape(experts, 2 * I, H).contiguous()
         act = torch.empty(rows, I, dtype=torch.bfloat16, device=DEV)
-        ops.moe_gemm_tc(a, inter.to(DEV), act, block_expert, swiglu=True, block_rows=block)
+        ops.moe_gemm_tc(a, inter.to(DEV), act, block_expert, swiglu=True, block_rows=block, tile_n=tile_n)
         for t in range(0, T, max(1, T // 7)):
             e = int(choice[t, 0])
             xin = x[t].double()
