@@ -8,7 +8,7 @@ comes from the file; a key that is absent means the mechanism is absent.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import asdict, dataclass
 from typing import Any, Mapping, Optional, Tuple
 
 from .errors import ConfigError, UnsupportedConfig
@@ -113,6 +113,9 @@ class SufolixConfig:
     streams: Optional[int]       # None: one plain residual stream
     layers: Tuple[SufolixLayer, ...]
     max_positions: int = DEFAULT_MAX_POSITIONS
+
+    def to_dict(self) -> dict:
+        return asdict(self)
 
     @classmethod
     def from_dict(cls, raw: Mapping[str, Any]) -> "SufolixConfig":

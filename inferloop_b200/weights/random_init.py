@@ -12,7 +12,7 @@ from __future__ import annotations
 import hashlib
 import json
 import os
-from typing import Any, Dict, Mapping, Sequence
+from typing import Any, Dict, Mapping, Optional, Sequence
 
 import torch
 
@@ -116,10 +116,12 @@ def random_weights(decls: Sequence[WeightDecl], seed: int, compute_dtype: torch.
 
 
 def write_random_model(folder: str, config: Mapping[str, Any], seed: int,
-                       dtype: torch.dtype = torch.float32, prefix: str = "model.",
+                       dtype: torch.dtype = torch.float32, prefix: Optional[str] = None,
                        registry=None) -> str:
     """Write `config.json` and `model.safetensors` for the architecture that `config`
-    names.  Every tensor, norm weights and biases included, is stored in `dtype`."""
+    names.  Every tensor, norm weights and biases included, is stored in `dtype`.  `prefix`
+    is put before every name that is not a root name: by default "model." where the
+    architecture's loader looks there, else the first prefix it looks under."""
     from ..config.registry import read_model_config
     from ..models.decoder import declare_weights
 
@@ -127,6 +129,8 @@ def write_random_model(folder: str, config: Mapping[str, Any], seed: int,
     _, _, spec = read_model_config(text, registry)
     os.makedirs(folder, exist_ok=True)
     decls = declare_weights(spec)
+    if prefix is None:
+        prefix = "model." if "model." in spec.weight_prefixes else spec.weight_prefixes[0]
 
     def items():
         for d in decls:

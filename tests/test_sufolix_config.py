@@ -96,3 +96,23 @@ def test_a_random_folder_round_trips_and_optional_tensors_may_be_left_out(tmp_pa
     tensors, ignored = load_weights(path, declare_weights(spec), spec.weight_prefixes, spec.embedding_name, torch.float32, "cpu")
     assert "l0.mix.vmix" not in tensors and "l1.mix.vmix" in tensors and not ignored
     assert tensors["l1.hc1.mix"].dtype == torch.float32 and tensors["l1.mix.q"].dtype == torch.float32
+
+
+def test_the_command_line_writes_and_inspects_a_sufolix_folder(tmp_path):
+    import subprocess
+    import sys
+    from helpers import ROOT
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(cases.CONFIG_S))
+    infer = os.path.join(ROOT, "bin", "infer")
+    out = subprocess.run([sys.executable, infer, "write-random-model", "--config", str(cfg), "--seed", "4", "--out", str(tmp_path / "m")],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    out = subprocess.run([sys.executable, infer, "inspect-model", str(tmp_path / "m")], capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stderr
+    info = json.loads(out.stdout)
+    assert info["architecture"] == "sufolix" and info["config"]["streams"] == 4
+    assert [l["feed_forward"] for l in info["layers"]] == ["routed_experts", "swiglu"]
+    assert [l["block"] for l in info["layers"]] == ["hyper_connections"] * 2
+    from inferloop_b200.weights.safetensors_io import SafetensorsFile
+    assert "embed" in SafetensorsFile(str(tmp_path / "m" / "model.safetensors")).names()      # no prefix for this architecture

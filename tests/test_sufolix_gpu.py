@@ -194,6 +194,22 @@ def test_greedy_generation_through_the_entry_point(root, name, dtype):
     assert info["running"] == 0 and all(g["free"] == g["total"] for g in info["cache"]["groups"])
 
 
+def test_the_command_line_generates_from_a_sufolix_folder(root):
+    import json, os, subprocess, sys
+    from helpers import ROOT
+    name, dtype = "R", "float32"
+    prompt = tokens_for(root, name, dtype, 9, 41)
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "infer"), "generate", cases.folder(root, name, stored(dtype)),
+                          "--tokens", ",".join(map(str, prompt)), "--max-new-tokens", "6", "--dtype", dtype, "--block-size", "16",
+                          "--num-gpu-blocks-override", "8"], capture_output=True, text=True, timeout=900)
+    assert out.returncode == 0, out.stderr
+    got = json.loads(out.stdout.strip().splitlines()[-1])["tokens"]
+    model = cases.plain_model(root, name, stored(dtype))
+    ref = model.forward(list(prompt) + got)[len(prompt) - 1:-1]
+    for i, tok in enumerate(got):
+        assert ref[i, tok] >= ref[i].max() - 2e-5 * float(ref.abs().max())
+
+
 def test_the_trace_program_replays_a_sufolix_folder(root, tmp_path):
     from helpers import run_trace_program
     name, dtype = "S", "float32"
