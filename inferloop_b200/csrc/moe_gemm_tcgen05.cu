@@ -11,8 +11,9 @@
 // accumulators with tcgen05.ld and write the rows out.  Tile shapes: 128 rows x 128 weight
 // rows, two CTAs to an SM so that one tile's write-out runs under the other's products (few
 // rows per expert: the launch streams the chosen experts' weights); 128 x 256 with a ring of four
-// stages; and 256 x 256 (two 128-row accumulators that share every weight block, all 512 columns
-// of tensor memory): wider tiles need fewer operand bytes per flop.  The weight tile of group
+// stages, one tile a CTA or (the default for many rows) persistent CTAs with two accumulators;
+// and 256 x 256 (two 128-row accumulators that share every weight block, all 512 columns of
+// tensor memory): wider tiles need fewer operand bytes per flop.  The weight tile of group
 // g starts at row g * N + n0 of the stacked matrix; columns past N are not written, so a tile
 // that reaches into the next group's rows (or past the end, where TMA fills zeros) is harmless.
 // With the SwiGLU epilogue W holds blocks of 64 gate rows followed by their 64 up rows, a tile is
@@ -203,6 +204,152 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   }
 }
 
+// The same product with persistent CTAs, for launches of many tiles: one CTA an SM walks the
+// tiles blockIdx.x, blockIdx.x + gridDim.x, ... (weight tiles of a block of rows are neighbours, so
+// CTAs that run side by side share the rows' operand in L2), the operand ring runs on across the
+// tiles, and two accumulators of BN columns take turns: a tile is written out while the next one
+// is multiplied.  The blocks that hold rows are the first ones (csrc/moe.cu fills them in expert
+// order), so a CTA is done at the first block without a group.
+template <int BN, int kStages>
+__global__ void __launch_bounds__(192, 1)
+moe_gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const Params p,
+                           int n_blocks, int tiles_n) {
+  constexpr uint32_t kStageBytes = stage_bytes<1, BN>();
+  constexpr uint32_t kTmemCols = 2 * BN;           // 512 for BN = 256
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * kStages, tfull0 = empty0 + 8 * kStages, tempty0 = tfull0 + 16;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* failed = reinterpret_cast<volatile int*>(bars + 2 * kStages + 5);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long total = (long long)n_blocks * tiles_n;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 128); }
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // the tile after `t` of this CTA, or false when there is none
+  auto tile_at = [&](long long t, int& b, int& n0, int& g) {
+    if (t >= total) return false;
+    b = (int)(t / tiles_n);
+    n0 = (int)(t % tiles_n) * BN;
+    g = __ldg(p.block_group + b);
+    return g >= 0;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {                             // ---- TMA producer
+      bool ok = true;
+      uint32_t it = 0;
+      int b, n0, g;
+      for (long long t = blockIdx.x; ok && tile_at(t, b, n0, g); t += gridDim.x) {
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % kStages;
+          if (it >= (uint32_t)kStages) {
+            ok = mbar_wait(empty0 + 8 * s, ((it / kStages) - 1) & 1);
+            if (!ok) break;
+          }
+          const uint32_t dst = base + s * kStageBytes;
+          mbar_expect_tx(full0 + 8 * s, kStageBytes);
+          tma_load_2d(dst, &map_a, full0 + 8 * s, kb * kBlockK, b * kRows);
+          tma_load_2d(dst + kBytesA, &map_w, full0 + 8 * s, kb * kBlockK, g * p.N + n0);
+        }
+      }
+      if (!ok) { *failed = 1; if (p.error_flag) *p.error_flag = 1; }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {                             // ---- MMA issuer
+      constexpr uint32_t idesc = instr_desc(kRows, BN);
+      bool ok = true;
+      uint32_t it = 0, j = 0;
+      int b, n0, g;
+      for (long long t = blockIdx.x; ok && tile_at(t, b, n0, g); t += gridDim.x, ++j) {
+        const uint32_t buf = j & 1;
+        ok = mbar_wait(tempty0 + 8 * buf, ((j >> 1) & 1) ^ 1);     // the write-out has drained this accumulator
+        if (!ok) break;
+        tcgen05_fence_after();
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % kStages;
+          ok = mbar_wait(full0 + 8 * s, (it / kStages) & 1);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t a = base + s * kStageBytes;
+          const uint64_t da = smem_desc(a), db = smem_desc(a + kBytesA);
+#pragma unroll
+          for (int k = 0; k < kBlockK / 16; ++k) mma_bf16(tmem_base + buf * BN, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          tcgen05_commit(empty0 + 8 * s);
+        }
+        if (ok) tcgen05_commit(tfull0 + 8 * buf);
+      }
+      if (!ok) {
+        *failed = 1; if (p.error_flag) *p.error_flag = 1;
+        tcgen05_commit(tfull0); tcgen05_commit(tfull0 + 8);       // let the write-out leave its wait
+      }
+    }
+  } else {
+    // ---- write-out: warps 2..5 own tensor-memory lanes 32 (warp & 3) .. + 31, one row each
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    uint32_t j = 0;
+    int b, n0, g;
+    for (long long t = blockIdx.x; tile_at(t, b, n0, g); t += gridDim.x, ++j) {
+      const uint32_t buf = j & 1;
+      if (!mbar_wait(tfull0 + 8 * buf, (j >> 1) & 1)) { *failed = 1; if (p.error_flag) *p.error_flag = 1; }
+      tcgen05_fence_after();
+      if (*failed != 0) break;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN;
+      const size_t out_row = (size_t)(b * kRows + row) * p.ldo;
+      if (p.swiglu) {
+#pragma unroll 1
+        for (int pair = 0; pair < BN / 128; ++pair) {
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int c = n0 / 2 + pair * 64 + 32 * half;
+            if (c >= p.N / 2) continue;
+            float gt[32], up[32];
+            tmem_load_32(taddr + pair * 128 + 32 * half, gt);
+            tmem_load_32(taddr + pair * 128 + 64 + 32 * half, up);
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = silu_mul(gt[i], up[i]);
+            store32(p, out_row, c, p.N / 2, v);
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          const int c = n0 + c0;
+          if (c >= p.N) break;
+          float v[32];
+          tmem_load_32(taddr + c0, v);
+          store32(p, out_row, c, p.N, v);
+        }
+      }
+      tcgen05_fence_before();
+      mbar_arrive(tempty0 + 8 * buf);            // the accumulator may be written again
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
 struct MapKey {
   const void* ptr; long long rows; int cols, ld, box_rows;
   bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
@@ -256,6 +403,27 @@ static int launch_tiles(const void* A, const void* W, const Params& p, int rows,
   return check_launch("moe_gemm_tc");
 }
 
+template <int BN, int kStages>
+static int launch_persistent(const void* A, const void* W, const Params& p, int rows, int groups, int lda, cudaStream_t stream) {
+  static OncePerDevice once;
+  constexpr size_t smem = smem_bytes<1, BN, kStages>() + 64;
+  if (once.first() &&
+      cudaFuncSetAttribute(moe_gemm_persistent_kernel<BN, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    once.forget();
+    return fail("moe_gemm: cannot reserve %zu bytes of shared memory", smem);
+  }
+  CUtensorMap ma, mw;
+  if (make_map(&ma, A, rows, p.K, lda, kRows)) return -1;
+  if (make_map(&mw, W, (long long)groups * p.N, p.K, p.K, BN)) return -1;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  const int n_blocks = rows / kRows, tiles_n = (p.N + BN - 1) / BN;
+  const long long total = (long long)n_blocks * tiles_n;
+  ilb::launch(moe_gemm_persistent_kernel<BN, kStages>, dim3((unsigned)(total < sms ? total : sms)), dim3(192), smem, stream, ma, mw, p,
+              n_blocks, tiles_n);
+  return check_launch("moe_gemm_tc");
+}
+
 // Whether these sizes meet the TMA rules (rows of 16 bytes, 16-byte bases).
 ILB_EXPORT int ilb_moe_gemm_tc_supported(int N, int K, int lda, int swiglu) {
   return (K % 8 == 0 && lda % 8 == 0 && N > 0 && (!swiglu || N % 128 == 0)) ? 1 : 0;
@@ -263,13 +431,14 @@ ILB_EXPORT int ilb_moe_gemm_tc_supported(int N, int K, int lda, int swiglu) {
 
 // A: [rows, K] bf16 (leading dimension lda); W: [groups, N, K] bf16, contiguous; out: [rows, N]
 // (with swiglu: [rows, N / 2]) bf16 or f32 with leading dimension ldo; block_group: [rows / block_rows],
-// block_rows = 128 or 256; tile_n = 128 or 256 weight rows per tile (256 rows take 256).
+// block_rows = 128 or 256; tile_n = 128 or 256 weight rows per tile (256 rows take 256); tile_n = 257
+// asks for the persistent form of the 128 x 256 tile.
 ILB_EXPORT int ilb_moe_gemm_tc(const void* A, const void* W, void* out, int out_f32, int rows, int groups, int N, int K, int lda,
                                int ldo, int swiglu, const int* block_group, int block_rows, int tile_n, int* error_flag,
                                cudaStream_t stream) {
   ILB_REQUIRE(rows >= 0 && groups > 0 && N > 0 && K > 0, "moe_gemm: bad sizes rows=%d groups=%d N=%d K=%d", rows, groups, N, K);
   ILB_REQUIRE(block_rows == 128 || block_rows == 256, "moe_gemm: blocks of 128 or 256 rows, not %d", block_rows);
-  ILB_REQUIRE(tile_n == 256 || (tile_n == 128 && block_rows == 128), "moe_gemm: tiles of %d x %d are not built", block_rows, tile_n);
+  ILB_REQUIRE(tile_n == 256 || ((tile_n == 128 || tile_n == 257) && block_rows == 128), "moe_gemm: tiles of %d x %d are not built", block_rows, tile_n);
   ILB_REQUIRE(rows % block_rows == 0 && rows / block_rows <= 65535, "moe_gemm: rows must come in blocks of %d (at most 65535 blocks)", block_rows);
   ILB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && lda >= K && ((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0),
               "moe_gemm: operands must have rows of whole 16 bytes on 16-byte boundaries");
@@ -283,6 +452,7 @@ ILB_EXPORT int ilb_moe_gemm_tc(const void* A, const void* W, void* out, int out_
   p.N = N; p.K = K; p.ldo = ldo; p.k_blocks = (K + kBlockK - 1) / kBlockK;
   p.swiglu = swiglu ? 1 : 0; p.out_f32 = out_f32 ? 1 : 0;
   if (block_rows == 256) return launch_tiles<2, 256, 3>(A, W, p, rows, groups, lda, stream);
+  if (tile_n == 257) return launch_persistent<256, 4>(A, W, p, rows, groups, lda, stream);
   if (tile_n == 256) return launch_tiles<1, 256, 4>(A, W, p, rows, groups, lda, stream);
   return launch_tiles<1, 128, 3>(A, W, p, rows, groups, lda, stream);
 }

@@ -251,8 +251,8 @@ def moe_gemm_tc_eligible(a: torch.Tensor, w: torch.Tensor, swiglu: bool = False)
             and (not swiglu or w.shape[1] % 128 == 0))
 
 
-MOE_WIDE_BLOCKS = True     # blocks of 256 rows (256 x 256 tiles) once an expert gets a thousand rows on average
-MOE_TILE_N = 0             # tests and measurements force 128 or 256 weight rows per tile of 128 rows; 0: the default choice
+MOE_WIDE_BLOCKS = False    # blocks of 256 rows (256 x 256 tiles) once an expert gets a thousand rows on average: measured slower than the persistent 128 x 256 form
+MOE_TILE_N = 0             # tests and measurements force 128, 256 or 257 (256 with persistent CTAs) weight rows per tile of 128 rows; 0: the default choice
 
 
 def moe_gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, block_group: torch.Tensor, swiglu: bool = False,
@@ -271,8 +271,9 @@ def moe_gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, block_group
     if block_rows == GROUP_ROWS_TC_WIDE:
         tile_n = 256
     elif not tile_n:
-        # a tile of 256 weight rows halves the bytes of the rows' operand per flop; it pays once the rows are many
-        tile_n = MOE_TILE_N or (256 if M >= 2048 and N >= 512 else 128)
+        # many rows: persistent CTAs over 128 x 256 tiles with two accumulators (a tile is written out under the
+        # next one's products); few rows: 128 x 128 tiles, two CTAs an SM, a stream of the chosen experts' weights
+        tile_n = MOE_TILE_N or (257 if M >= 2048 and N >= 512 else 128)
     st = _tc_state(a.device)
     _call("moe_gemm_tcgen05", "ilb_moe_gemm_tc", _ptr(a), _ptr(w), _ptr(out), _i(1 if out.dtype == torch.float32 else 0), _i(M),
           _i(w.shape[0]), _i(N), _i(K), _i(a.stride(0)), _i(out.stride(0)), _i(1 if swiglu else 0), _ptr(block_group),

@@ -103,8 +103,8 @@ class RoutedExperts(FeedForward):
 
     def _block_rows(self, tokens: int) -> int:
         """Rows of a block of the sorted order: the exact product's 16, or the tensor-core
-        product's tile height: 128 rows, or 256 once an expert gets a thousand rows on average (measured:
-        at 2,048 tokens over 16 experts the tall tile is no faster, at 8,192 it is)."""
+        product's tile height: 128 rows (256 only when `ops.MOE_WIDE_BLOCKS` is set: measured slower than
+        persistent CTAs over 128-row tiles at every size tried)."""
         fused = self.ctx.dtype == torch.bfloat16 and self.inter % 64 == 0 and self.hidden % 8 == 0
         if not fused:
             return ops.GROUP_ROWS_SIMT

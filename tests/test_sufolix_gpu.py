@@ -396,7 +396,7 @@ def test_router_logits_are_32_bit_sums(dtype, T, rows, width):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("block,tile_n", [(16, 0), (128, 128), (128, 256), (256, 256)])
+@pytest.mark.parametrize("block,tile_n", [(16, 0), (128, 128), (128, 256), (128, 257), (256, 256)])     # 257: persistent CTAs, 128 x 256 tiles
 @pytest.mark.parametrize("T,experts,top,H,I", [(1, 4, 2, 64, 64), (9, 5, 2, 96, 128), (300, 8, 1, 256, 64), (77, 3, 3, 128, 192),
                                                (700, 2, 2, 320, 384)])
 def test_sorted_rows_grouped_products_and_the_sum(dtype, block, tile_n, T, experts, top, H, I):
