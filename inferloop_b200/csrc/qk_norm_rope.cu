@@ -132,13 +132,19 @@ __device__ __forceinline__ uint4 pack8(const float* x) {
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// kVariant: the modes of the general kernel (pairs of neighbours over the first rotary_dim
+// elements, which a lane's eight consecutive elements hold four of; the norm after the rotation;
+// no weight) and the kept / mixed values.
+template <bool kVariant>
 __global__ void __launch_bounds__(kFastWarps * 32)
 qk_norm_rope_d128_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
                          const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
                          const float2* __restrict__ rope_table, const int* __restrict__ positions,
                          const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int max_blocks,
                          int page_size, int num_pages, __nv_bfloat16* __restrict__ k_cache,
-                         __nv_bfloat16* __restrict__ v_cache, int nq, int nkv, int qkv_stride, int q_out_stride) {
+                         __nv_bfloat16* __restrict__ v_cache, int nq, int nkv, int qkv_stride, int q_out_stride,
+                         int mode, int rotary_dim, int v_mode, const float* __restrict__ v_lambda,
+                         __nv_bfloat16* __restrict__ v_first) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
   constexpr int d = 128;
@@ -183,9 +189,20 @@ qk_norm_rope_d128_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* _
     }
     return cache_state == 1;
   };
-  // cos and sin of this lane's eight pairs (j, j + 64), j = 8 l8 .. 8 l8 + 7
+  // cos and sin of this lane's eight pairs (j, j + 64), j = 8 l8 .. 8 l8 + 7; with pairs of
+  // neighbours: of the pairs 4 l8 .. 4 l8 + 3 (lower half) and 32 + 4 l8 .. (upper half)
   float2 cs[8];
-  if (rope_table != nullptr) {
+  if (kVariant && (mode & kPairsInterleaved)) {
+    if (rope_table != nullptr) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int pair = 32 * h + 4 * l8 + i;
+          cs[4 * h + i] = 2 * pair + 1 < rotary_dim ? __ldg(rope_table + (size_t)t * (rotary_dim / 2) + pair) : make_float2(1.f, 0.f);
+        }
+    }
+  } else if (rope_table != nullptr) {
     const float4* c = reinterpret_cast<const float4*>(rope_table + (size_t)t * (d / 2) + 8 * l8);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -208,6 +225,74 @@ qk_norm_rope_d128_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* _
     unpack8(raw[u][0], x);
     unpack8(raw[u][1], x + 8);
     const float* w = is_q ? q_weight : (is_k ? k_weight : nullptr);
+    if constexpr (kVariant) {
+      const bool turn = (is_q || is_k) && rope_table != nullptr;
+      const bool normed = (is_q || is_k) && (w != nullptr || (mode & kNormUnweighted));
+      auto rotate = [&]() {
+        if (mode & kPairsInterleaved) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {                      // (x[2 i], x[2 i + 1]) is pair i of this lane
+            const float a = x[2 * i], b = x[2 * i + 1];
+            x[2 * i] = __fsub_rn(__fmul_rn(a, cs[i].x), __fmul_rn(b, cs[i].y));
+            x[2 * i + 1] = __fadd_rn(__fmul_rn(a, cs[i].y), __fmul_rn(b, cs[i].x));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float a = x[i], b = x[8 + i];
+            x[i] = __fsub_rn(__fmul_rn(a, cs[i].x), __fmul_rn(b, cs[i].y));
+            x[8 + i] = __fadd_rn(__fmul_rn(a, cs[i].y), __fmul_rn(b, cs[i].x));
+          }
+        }
+      };
+      const bool after = mode & kNormAfterRotation;
+      if (turn && after) rotate();
+      // (every lane takes part in the exchange; a head past the end holds zeros)
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) ss = fmaf(x[i], x[i], ss);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+      if (!valid) continue;
+      if (normed) {
+        const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+        if (w != nullptr) {
+          float wl[8], wh[8];
+          weight8(w, 0, wl);
+          weight8(w, 1, wh);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { x[i] = x[i] * inv * wl[i]; x[8 + i] = x[8 + i] * inv * wh[i]; }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) x[i] = x[i] * inv;
+        }
+      }
+      if (turn && !after) rotate();
+      __nv_bfloat16* dst;
+      if (is_q) dst = q_out + (size_t)t * q_out_stride + (size_t)head * d;
+      else {
+        if (!is_k && v_mode != 0) {                          // this token's values of the first mixing layer
+          uint4* keep = reinterpret_cast<uint4*>(v_first + ((size_t)t * nkv + (head - nq - nkv)) * d);
+          if (v_mode == 1) {
+            keep[l8] = pack8(x);
+            keep[8 + l8] = pack8(x + 8);
+          } else {
+            const float lam = __ldg(v_lambda);
+            float f[16];
+            unpack8(keep[l8], f);
+            unpack8(keep[8 + l8], f + 8);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) x[i] = fmaf(lam, f[i], (1.0f - lam) * x[i]);
+          }
+        }
+        if (!cache_row()) continue;
+        dst = (is_k ? k_cache : v_cache) + cache_off + (size_t)(is_k ? head - nq : head - nq - nkv) * page_size * d;
+      }
+      reinterpret_cast<uint4*>(dst)[l8] = pack8(x);
+      reinterpret_cast<uint4*>(dst)[8 + l8] = pack8(x + 8);
+      continue;
+    }
     // (every lane takes part in the exchange; a head past the end holds zeros)
     float ss = 0.f;
 #pragma unroll
@@ -272,8 +357,9 @@ ILB_EXPORT int ilb_qk_norm_rope_cache(
   ILB_REQUIRE(v_mode == 0 || v_first != nullptr, "qk_norm_rope: value mixing needs the buffer of the first values");
   ILB_REQUIRE(v_mode != 2 || v_lambda != nullptr, "qk_norm_rope: value mixing needs its coefficient");
   if (n_tokens == 0) return 0;
-  if (dtype == kBF16 && (cache_dtype == kBF16 || k_cache == nullptr) && d == 128 && dv == 128 && mode == 0 && v_mode == 0 &&
-      (rope_table == nullptr || rotary_dim == d) &&
+  const bool stock = mode == 0 && v_mode == 0;
+  if (dtype == kBF16 && (cache_dtype == kBF16 || k_cache == nullptr) && d == 128 && dv == 128 &&
+      (rope_table == nullptr || rotary_dim == d || (mode & kPairsInterleaved)) && ((uintptr_t)v_first % 16 == 0) &&
       qkv_stride % 8 == 0 && q_out_stride % 8 == 0 && ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
       ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0) && ((uintptr_t)rope_table % 16 == 0) &&
       ((uintptr_t)q_weight % 16 == 0) && ((uintptr_t)k_weight % 16 == 0)) {
@@ -283,10 +369,17 @@ ILB_EXPORT int ilb_qk_norm_rope_cache(
     int ny = (heads + per_pass * kFastUnroll - 1) / (per_pass * kFastUnroll);
     const int most = (heads + per_pass - 1) / per_pass;
     while (ny < most && (long long)n_tokens * ny < 1184) ++ny;
-    ilb::launch(qk_norm_rope_d128_kernel, dim3(n_tokens, ny), dim3(kFastWarps * 32), 0, stream,
-                (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, q_weight, k_weight, eps, (const float2*)rope_table,
-                positions, seq_of_token, block_table, max_blocks, page_size, num_pages, (__nv_bfloat16*)k_cache,
-                (__nv_bfloat16*)v_cache, nq, nkv, qkv_stride, q_out_stride);
+    if (stock)
+      ilb::launch(qk_norm_rope_d128_kernel<false>, dim3(n_tokens, ny), dim3(kFastWarps * 32), 0, stream,
+                  (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, q_weight, k_weight, eps, (const float2*)rope_table,
+                  positions, seq_of_token, block_table, max_blocks, page_size, num_pages, (__nv_bfloat16*)k_cache,
+                  (__nv_bfloat16*)v_cache, nq, nkv, qkv_stride, q_out_stride, 0, d, 0, (const float*)nullptr, (__nv_bfloat16*)nullptr);
+    else
+      ilb::launch(qk_norm_rope_d128_kernel<true>, dim3(n_tokens, ny), dim3(kFastWarps * 32), 0, stream,
+                  (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, q_weight, k_weight, eps, (const float2*)rope_table,
+                  positions, seq_of_token, block_table, max_blocks, page_size, num_pages, (__nv_bfloat16*)k_cache,
+                  (__nv_bfloat16*)v_cache, nq, nkv, qkv_stride, q_out_stride, mode, rope_table ? rotary_dim : 0, v_mode, v_lambda,
+                  (__nv_bfloat16*)v_first);
     return check_launch("qk_norm_rope_cache");
   }
   dim3 grid(n_tokens, (nq + 2 * nkv + kWarpsPerBlock - 1) / kWarpsPerBlock);

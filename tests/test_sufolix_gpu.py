@@ -269,7 +269,8 @@ def test_streams_read_and_write(streams, width, out_dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("nq,nkv,d,dv,rd", [(6, 3, 16, 24, 8), (4, 1, 32, 16, 32), (2, 2, 64, 64, 2), (8, 2, 128, 128, 128)])
+@pytest.mark.parametrize("nq,nkv,d,dv,rd", [(6, 3, 16, 24, 8), (4, 1, 32, 16, 32), (2, 2, 64, 64, 2), (8, 2, 128, 128, 128),
+                                            (5, 5, 128, 128, 64), (3, 1, 128, 128, 6)])
 def test_rotation_of_neighbours_norm_after_it_and_mixed_values(dtype, nq, nkv, d, dv, rd):
     """The projection output through the fused kernel in the order rotation (pairs of neighbours) ->
     root-mean-square division, with the values kept by a first layer and mixed by a later one, into
