@@ -1,9 +1,11 @@
 // Fused per-head q/k RMSNorm + rotary position encoding + paged KV-cache write.
 //
-// Input is the fused projection output qkv[T, (nq + 2*nkv) * d].  For every token and
+// Input is the fused projection output qkv[T, (nq + nkv) * d + nkv * dv].  For every token and
 // head this kernel, in 32-bit:
-//   q, k heads: optional RMSNorm over the head (weight [d] shared by all heads), then the
-//               half-split rotation of the first `rotary_dim` elements;
+//   q, k heads: optional RMSNorm over the head (weight [d] shared by all heads, or none), and
+//               the rotation of the first `rotary_dim` elements (pairs i / i + rd/2, or
+//               neighbours 2i / 2i + 1), in either order;
+//   v heads:    optionally kept for, or mixed with, the values of the first mixing layer;
 //   q -> q_out[T, nq*d];  k, v -> the cache page of the token's position.
 // The reference runs these as three launches (norm_rows, prefill_rope, attention::append;
 // crates/backend/cuda-kernels/src/tile/state/aux_kernels.rs:104-200 and
@@ -12,7 +14,7 @@
 // x[i] = a cos - b sin, x[i + rd/2] = a sin + b cos
 // (crates/testing/cpu/reference-ops/src/kernels.rs:217-241).
 //
-// Cache layout per layer: K and V each [num_pages, nkv, page_size, d]; the page of
+// Cache layout per layer: K [num_pages, nkv, page_size, d], V [num_pages, nkv, page_size, dv]; the page of
 // position p of sequence s is block_table[s, p / page_size].
 #include "common.cuh"
 
