@@ -33,6 +33,9 @@ from .pages import OutOfPages, OwnerIds, PageLedgerError, PagePool, raise_for
 from .slots import OutOfSlots, SlotPool
 
 
+MODEL_OWNER = (-1, 0)          # owner of the state that belongs to the model as a whole, not to a layer
+
+
 @dataclass
 class LayerCache:
     """What a mixer gets: its keys/values (or None), the group whose block table applies,
@@ -44,6 +47,7 @@ class LayerCache:
     v: Optional[torch.Tensor]
     writable: bool
     state: Dict[str, torch.Tensor] = field(default_factory=dict)
+    instance: int = 0          # which run of a layer that runs several times (RunEntry.instance)
 
 
 @dataclass
@@ -66,9 +70,12 @@ class CacheManager:
     def __init__(self, layer_needs: Sequence[CacheNeeds], page_size: int, num_pages,
                  max_requests: int, dtype: torch.dtype = torch.float32,
                  device: Optional[torch.device] = None,
-                 run_order: Optional[Sequence[RunEntry]] = None) -> None:
+                 run_order: Optional[Sequence[RunEntry]] = None,
+                 model_slots: Sequence[SlotStateNeed] = ()) -> None:
         """`num_pages`: one number for every page group, or one number per group in the
-        order of :meth:`group_needs` (a group that reads a window needs fewer)."""
+        order of :meth:`group_needs` (a group that reads a window needs fewer).
+        `model_slots`: state per request that belongs to no layer (the embedding's), found
+        under :meth:`model_state`."""
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.page_size = int(page_size)
@@ -77,14 +84,15 @@ class CacheManager:
         self.layer_needs = list(layer_needs)
         n_layers = len(self.layer_needs)
         order = list(run_order) if run_order is not None else [RunEntry(i, i) for i in range(n_layers)]
-        # Only layers that some entry names as cache owner hold memory.
-        owners = sorted({e.cache_of for e in order})
+        # Only layers that some entry names as cache owner hold memory; a layer that runs
+        # several times with a cache per run owns one per (layer, instance).
+        owners = sorted({(e.cache_of, e.instance) for e in order})
         self.groups: List[PageGroup] = []
         self._group_of_layer: Dict[int, int] = {}
         self._index_in_group: Dict[int, int] = {}
         found: List[Tuple[PagedKVNeed, List[int]]] = []
-        for layer in owners:
-            need = self.layer_needs[layer].paged
+        for owner in owners:
+            need = self.layer_needs[owner[0]].paged
             if need is None:
                 continue
             for gi, (n, layers) in enumerate(found):
@@ -93,9 +101,9 @@ class CacheManager:
             else:
                 gi = len(found)
                 found.append((need, []))
-            self._group_of_layer[layer] = gi
-            self._index_in_group[layer] = len(found[gi][1])
-            found[gi][1].append(layer)
+            self._group_of_layer[owner] = gi
+            self._index_in_group[owner] = len(found[gi][1])
+            found[gi][1].append(owner[0])
         if isinstance(num_pages, (list, tuple)):
             if len(num_pages) != len(found):
                 raise ValueError(f"{len(num_pages)} pool sizes for {len(found)} page groups")
@@ -124,21 +132,21 @@ class CacheManager:
                 g.storage = torch.zeros(
                     (len(g.layers), 2 if both else 1, g.pool.num_pages, g.need.kv_heads, self.page_size, g.need.head_dim),
                     dtype=dtype, device=device)
-                if not both:
+                if not both and g.need.value_dim > 0:        # (value size 0: one vector per token, no values beside it)
                     g.storage_v = torch.zeros(
                         (len(g.layers), g.pool.num_pages, g.need.kv_heads, self.page_size, g.need.value_dim),
                         dtype=dtype, device=device)
         # fixed-size state
         self.slots = SlotPool(max_requests, _handle=self._lib.ilb_ledger_slots(self._h), _ids=self._ids)
-        self._slot_state: Dict[Tuple[int, str], torch.Tensor] = {}
-        self._slot_needs: Dict[int, Tuple[SlotStateNeed, ...]] = {}
-        for layer in owners:
-            needs = self.layer_needs[layer].slots
+        self._slot_state: Dict[Tuple[object, str], torch.Tensor] = {}
+        self._slot_needs: Dict[object, Tuple[SlotStateNeed, ...]] = {}
+        for owner in owners + ([MODEL_OWNER] if model_slots else []):
+            needs = tuple(model_slots) if owner == MODEL_OWNER else self.layer_needs[owner[0]].slots
             if needs:
-                self._slot_needs[layer] = tuple(needs)
+                self._slot_needs[owner] = tuple(needs)
                 if device is not None:
                     for need in needs:
-                        self._slot_state[(layer, need.name)] = torch.zeros(
+                        self._slot_state[(owner, need.name)] = torch.zeros(
                             (max_requests,) + tuple(need.shape), dtype=need.dtype, device=device)
         self._live: Dict[Hashable, int] = {}        # request -> its number in the ledger
 
@@ -155,7 +163,7 @@ class CacheManager:
         needs = list(layer_needs)
         order = list(run_order) if run_order is not None else [RunEntry(i, i) for i in range(len(needs))]
         found: List[Tuple[PagedKVNeed, List[int]]] = []
-        for layer in sorted({e.cache_of for e in order}):
+        for layer, _ in sorted({(e.cache_of, e.instance) for e in order}):
             need = needs[layer].paged
             if need is None:
                 continue
@@ -270,17 +278,25 @@ class CacheManager:
         return m
 
     def layer_cache(self, entry: RunEntry) -> LayerCache:
-        owner = entry.cache_of
+        owner = (entry.cache_of, entry.instance)
         gi = self._group_of_layer.get(owner)
         k = v = None
         if gi is not None and self.groups[gi].storage is not None:
             g = self.groups[gi]
             s = g.storage[self._index_in_group[owner]]
             k = s[0]
-            v = s[1] if g.storage_v is None else g.storage_v[self._index_in_group[owner]]
+            if g.storage_v is not None:
+                v = g.storage_v[self._index_in_group[owner]]
+            elif g.need.value_dim == g.need.head_dim:
+                v = s[1]
         state = {need.name: self._slot_state[(owner, need.name)]
                  for need in self._slot_needs.get(owner, ()) if (owner, need.name) in self._slot_state}
-        return LayerCache(owner, gi, self.page_size, k, v, entry.writes_cache, state)
+        return LayerCache(entry.cache_of, gi, self.page_size, k, v, entry.writes_cache, state, entry.instance)
+
+    def model_state(self) -> Dict[str, torch.Tensor]:
+        """The state per request that belongs to no layer: name -> [slots, *shape]."""
+        return {need.name: self._slot_state[(MODEL_OWNER, need.name)]
+                for need in self._slot_needs.get(MODEL_OWNER, ()) if (MODEL_OWNER, need.name) in self._slot_state}
 
     # ------------------------------------------------------------------ facts
     def free_pages(self) -> Dict[int, int]:

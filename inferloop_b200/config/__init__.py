@@ -2,10 +2,11 @@ from .errors import ConfigError, UnsupportedConfig
 from .spec import PartSpec, LayerSpec, RunEntry, ModelSpec
 from .qwen3 import Qwen3Config
 from .sufolix import SufolixConfig
+from .mamevik import MamevikConfig
 from .registry import Architecture, ArchitectureRegistry, default_registry, read_model_config
 
 __all__ = [
     "ConfigError", "UnsupportedConfig", "PartSpec", "LayerSpec", "RunEntry", "ModelSpec",
-    "Qwen3Config", "SufolixConfig", "Architecture", "ArchitectureRegistry", "default_registry",
+    "Qwen3Config", "SufolixConfig", "MamevikConfig", "Architecture", "ArchitectureRegistry", "default_registry",
     "read_model_config",
 ]

@@ -100,8 +100,10 @@ def default_registry() -> ArchitectureRegistry:
         _DEFAULT = ArchitectureRegistry()
         from ..models.qwen3 import ARCHITECTURE
         from ..models.sufolix import ARCHITECTURE as SUFOLIX
+        from ..models.mamevik import ARCHITECTURE as MAMEVIK
         _DEFAULT.register(ARCHITECTURE)
         _DEFAULT.register(SUFOLIX)
+        _DEFAULT.register(MAMEVIK)
     return _DEFAULT
 
 

@@ -54,9 +54,11 @@ class LayerSpec:
 
     prefix: str                 # e.g. "model.layers.3."
     block: PartSpec             # arrangement of the parts, e.g. kind "pre_norm"
-    mixer: PartSpec             # token mixer, e.g. kind "gqa_attention"
-    feed_forward: PartSpec      # e.g. kind "swiglu"; kind "none" for a layer that has only its mixer
-    norm: PartSpec              # norm used by the block, e.g. kind "rms"
+    # A block that is not mixer + feed-forward (one that maps the residual stream between
+    # layers, say) leaves the three below at their defaults.
+    mixer: PartSpec = PartSpec("none")         # token mixer, e.g. kind "gqa_attention"
+    feed_forward: PartSpec = PartSpec("none")  # e.g. kind "swiglu"; kind "none" for a layer that has only its mixer
+    norm: PartSpec = PartSpec("none")          # norm used by the block, e.g. kind "rms"
 
 
 @dataclass(frozen=True)
@@ -65,12 +67,16 @@ class RunEntry:
 
     `layer` indexes :attr:`ModelSpec.layers`.  `cache_of` is the layer whose cache the
     mixer reads and writes; it equals `layer` unless this entry borrows another
-    layer's cache.  `writes_cache` is False for an entry that only reads it.
+    layer's cache.  `writes_cache` is False for an entry that only reads it.  `instance`
+    tells apart the runs of a layer that is run several times with the same weights, each
+    run with a cache and state of its own (a loop over a span of layers): the cache's owner
+    is the pair (`cache_of`, `instance`), and a block reads the number as `cache.instance`.
     """
 
     layer: int
     cache_of: int
     writes_cache: bool = True
+    instance: int = 0
 
 
 @dataclass(frozen=True)
@@ -100,6 +106,11 @@ class ModelSpec:
     # embedding fills all of them, the blocks see [tokens, residual_streams * hidden_size], and
     # their sum is what the final norm reads.
     residual_streams: int = 1
+    # A part of role "embedding" that turns the step's token ids into the first residual
+    # stream (None: one row of the token table per token, times `embedding_scale`).  It may
+    # keep state per request (model-level slot state) and leave what it made in a workspace
+    # buffer for later blocks.
+    embedding: Optional[PartSpec] = None
 
     def __post_init__(self) -> None:
         if self.residual_streams < 1:
@@ -113,10 +124,12 @@ class ModelSpec:
         for e in self.run_order:
             if not (0 <= e.layer < n and 0 <= e.cache_of < n):
                 raise ValueError(f"run order entry {e} names a layer outside 0..{n - 1}")
+            if e.instance < 0:
+                raise ValueError(f"run order entry {e} has a negative instance")
             if e.writes_cache:
-                owners_written.add(e.cache_of)
+                owners_written.add((e.cache_of, e.instance))
         for e in self.run_order:
-            if not e.writes_cache and e.cache_of not in owners_written:
+            if not e.writes_cache and (e.cache_of, e.instance) not in owners_written:
                 raise ValueError(
                     f"run order entry {e} reads the cache of layer {e.cache_of}, "
                     "which no entry writes")

@@ -216,6 +216,7 @@ struct PrefillParams {
   const int* positions; const int* cu_q; const int* block_table;
   int max_blocks, n_seqs, nq, window, q_stride, out_stride;
   float scale_log2;
+  const float* sink;   // [nq] or null: a logit per query head that joins the softmax's denominator unscaled, without a value
 };
 
 template <int D>
@@ -295,6 +296,11 @@ prefill_kernel(const PrefillParams p) {
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
     if (!live[r]) continue;
+    if (p.sink != nullptr && st.m[r] != -INFINITY) {
+      // the running maximum stays that of the keys: the sink only adds its term, and a learned logit is never so far
+      // above the scores that 2^(sink - m) leaves the 32-bit range
+      l += exp2f(p.sink[head[r]] * kLog2e - st.m[r]);
+    }
     const float inv = l > 0.f ? 1.f / l : 0.f;
     __nv_bfloat16* dst = p.out + (size_t)tok[r] * p.out_stride + (size_t)head[r] * D;
 #pragma unroll
@@ -312,6 +318,7 @@ struct DecodeParams {
   int* tickets;        // [seqs * nkv], zero between launches
   int max_blocks, n_seqs, nq, window, q_stride, out_stride, chunk, max_chunks, rows16;
   float scale_log2;
+  const float* sink;   // as in PrefillParams
 };
 
 template <int D>
@@ -418,7 +425,8 @@ decode_kernel(const DecodeParams p) {
     for (int idx = threadIdx.x; idx < G * D; idx += kWarps * 32) {
       const int h = idx / D, c = idx % D;
       const float* rec = rec_base + ((size_t)chunk_i * G + h) * kRec;
-      const float l = rec[D + 1];
+      float l = rec[D + 1];
+      if (p.sink != nullptr && rec[D] != -INFINITY) l += exp2f(p.sink[kvh * G + h] * kLog2e - rec[D]);
       p.out[(size_t)tok * p.out_stride + (size_t)(kvh * G + h) * D + c] = __float2bfloat16_rn(l > 0.f ? rec[c] / l : 0.f);
     }
     return;
@@ -464,6 +472,7 @@ decode_kernel(const DecodeParams p) {
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) l_all += __shfl_xor_sync(0xffffffffu, l_all, o);
+    if (p.sink != nullptr && m_all != -INFINITY) l_all += exp2f(p.sink[kvh * G + h] * kLog2e - m_all);
     const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
     __syncwarp();
     for (int ci = lane; ci < n_chunks; ci += 32) fw[h * n_chunks + ci] *= inv;
@@ -546,7 +555,7 @@ ILB_EXPORT int ilb_attention_prefill(const void* q, void* out, const void* k_cac
                                      const int* positions, const int* cu_q, const int* block_table,
                                      int max_blocks, int page_size, int num_pages, int window, float scale,
                                      int n_seqs, int n_tiles, int nq, int nkv, int d, int q_stride, int out_stride,
-                                     cudaStream_t stream) {
+                                     const float* sink, cudaStream_t stream) {
   ILB_REQUIRE(ilb_attention_flash_supported(d), "attention prefill: head size %d is not built (32, 64, 96, 128 are)", d);
   ILB_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention prefill: %d query heads are not a multiple of %d kv heads", nq, nkv);
   ILB_REQUIRE(n_seqs > 0 && n_tiles > 0 && nkv <= 65535, "attention prefill: bad grid");
@@ -555,7 +564,7 @@ ILB_EXPORT int ilb_attention_prefill(const void* q, void* out, const void* k_cac
               ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0), "attention prefill: misaligned operands");
   PrefillParams p{(const __nv_bfloat16*)q, (__nv_bfloat16*)out,
                   Cache{(const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, page_size, num_pages, nkv},
-                  positions, cu_q, block_table, max_blocks, n_seqs, nq, window, q_stride, out_stride, scale * kLog2e};
+                  positions, cu_q, block_table, max_blocks, n_seqs, nq, window, q_stride, out_stride, scale * kLog2e, sink};
   switch (d) {
     case 32: return launch_prefill<32>(p, n_tiles, stream);
     case 64: return launch_prefill<64>(p, n_tiles, stream);
@@ -570,7 +579,7 @@ ILB_EXPORT int ilb_attention_decode(const void* q, void* out, const void* k_cach
                                     int max_blocks, int page_size, int num_pages, int window, float scale,
                                     int n_seqs, int nq, int nkv, int d, int q_stride, int out_stride,
                                     int chunk, int max_chunks, float* scratch, long long scratch_floats,
-                                    int* tickets, int n_tickets, cudaStream_t stream) {
+                                    int* tickets, int n_tickets, const float* sink, cudaStream_t stream) {
   ILB_REQUIRE(ilb_attention_flash_supported(d), "attention decode: head size %d is not built (32, 64, 96, 128 are)", d);
   ILB_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention decode: %d query heads are not a multiple of %d kv heads", nq, nkv);
   ILB_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && max_chunks > 0 && max_chunks <= 65535, "attention decode: bad grid");
@@ -594,7 +603,7 @@ ILB_EXPORT int ilb_attention_decode(const void* q, void* out, const void* k_cach
   DecodeParams p{(const __nv_bfloat16*)q, (__nv_bfloat16*)out,
                  Cache{(const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, page_size, num_pages, nkv},
                  positions, cu_q, block_table, scratch, tickets, max_blocks, n_seqs, nq, window, q_stride, out_stride,
-                 chunk, max_chunks, rows16, scale * kLog2e};
+                 chunk, max_chunks, rows16, scale * kLog2e, sink};
   switch (d) {
     case 32: return launch_decode<32>(p, stream);
     case 64: return launch_decode<64>(p, stream);
@@ -661,7 +670,7 @@ ILB_EXPORT int ilb_attention_decode_static(const void* q, void* out, const void*
   if (e != cudaSuccess) return fail("attention decode (static): clearing the counters failed: %s", cudaGetErrorString(e));
   return ilb_attention_decode(q, out, k_cache, v_cache, positions, cu_q, block_table, max_blocks, page_size, num_pages,
                               window, scale, n_seqs, nq, nkv, d, q_stride, out_stride, chunk, max_chunks, records,
-                              (long long)kStaticScratchFloats, tickets, (int)kStaticTickets, stream);
+                              (long long)kStaticScratchFloats, tickets, (int)kStaticTickets, nullptr, stream);
 }
 
 ILB_DEFINE_LAST_ERROR()

@@ -10,6 +10,9 @@
 // Keys and queries have head size d, values and the output dv (the V cache is
 // [pages, nkv, page_size, dv]).
 //
+// With `sink` (one learned logit per query head) the softmax's denominator also holds exp(sink):
+// a key that is always seen, has no value, and whose logit is taken as it is (no scale).
+//
 // Reference formula: s_j = q.k_j / sqrt(d), p = softmax(s), o = sum p_j v_j, query head h
 // uses kv head h / (nq / nkv); window start (p + 1).saturating_sub(w)
 // (crates/testing/cpu/reference-ops/src/kernels.rs:251-297).
@@ -19,7 +22,7 @@
 using namespace ilb;
 
 constexpr int kWarps = 4;
-constexpr int kMaxHeadDim = 256;
+constexpr int kMaxHeadDim = 512;
 
 template <typename TQ, typename TC>
 __global__ void __launch_bounds__(kWarps * 32)
@@ -28,7 +31,7 @@ paged_attention_simple_kernel(const TQ* __restrict__ q, TQ* __restrict__ out,
                               const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                               const int* __restrict__ block_table, int max_blocks, int page_size,
                               int num_pages, int window, float scale, int nq, int nkv, int d, int dv,
-                              int q_stride, int out_stride) {
+                              int q_stride, int out_stride, const float* __restrict__ sink) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
   __shared__ float qs[kMaxHeadDim];
@@ -96,11 +99,13 @@ paged_attention_simple_kernel(const TQ* __restrict__ q, TQ* __restrict__ out,
   __syncthreads();
   float m_all = -INFINITY;
   for (int w = 0; w < kWarps; ++w) m_all = fmaxf(m_all, red_m[w]);
+  if (sink != nullptr) m_all = fmaxf(m_all, sink[h]);
   float f[kWarps], l_all = 0.f;
   for (int w = 0; w < kWarps; ++w) {
     f[w] = (red_m[w] == -INFINITY) ? 0.f : expf(red_m[w] - m_all);
     l_all += red_l[w] * f[w];
   }
+  if (sink != nullptr) l_all += expf(sink[h] - m_all);
   for (int c = threadIdx.x; c < dv; c += blockDim.x) {
     float o = 0.f;
     for (int w = 0; w < kWarps; ++w) o += red_acc[w][c] * f[w];
@@ -114,7 +119,7 @@ ILB_EXPORT int ilb_paged_attention_simple(
     const void* q, void* out, int dtype, const void* k_cache, const void* v_cache, int cache_dtype,
     const int* positions, const int* seq_of_token, const int* block_table, int max_blocks,
     int page_size, int num_pages, int window, float scale, int n_tokens, int nq, int nkv, int d, int dv,
-    int q_stride, int out_stride, cudaStream_t stream) {
+    int q_stride, int out_stride, const float* sink, cudaStream_t stream) {
   ILB_REQUIRE(n_tokens >= 0 && nq > 0 && nkv > 0 && d > 0, "attention: bad sizes");
   ILB_REQUIRE(nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
   ILB_REQUIRE(dv > 0 && d <= kMaxHeadDim && dv <= kMaxHeadDim, "attention: head size %d / %d exceeds %d", d, dv, kMaxHeadDim);
@@ -128,7 +133,7 @@ ILB_EXPORT int ilb_paged_attention_simple(
   ilb::launch(paged_attention_simple_kernel<TQ, TC>, dim3(grid), dim3(kWarps * 32), 0, stream,                      \
       (const TQ*)q, (TQ*)out, (const TC*)k_cache, (const TC*)v_cache, positions, seq_of_token, \
       block_table, max_blocks, page_size, num_pages, window, scale, nq, nkv, d, dv, q_stride,  \
-      out_stride)
+      out_stride, sink)
   if (dtype == kF32 && cache_dtype == kF32) ILB_LAUNCH(float, float);
   else if (dtype == kBF16 && cache_dtype == kBF16) ILB_LAUNCH(__nv_bfloat16, __nv_bfloat16);
   else if (dtype == kF32 && cache_dtype == kBF16) ILB_LAUNCH(float, __nv_bfloat16);

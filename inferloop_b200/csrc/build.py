@@ -41,6 +41,8 @@ MODULES: Dict[str, List[str]] = {
     "hyper": [],
     "moe": [],
     "moe_gemm_tcgen05": [],
+    "ssm": [],
+    "latent": [],
 }
 
 _LOCK = threading.Lock()

@@ -334,4 +334,161 @@ ILB_EXPORT int ilb_decode_advance(int* tokens, int* positions, int* kv_len, cons
   return check_launch("decode_advance");
 }
 
+// ---------------------------------------------------------------- gated unit with clamped halves
+// out = a(g) * (u + up_offset), a(g) = g * sigmoid(sharpness * g), g = min(gate, limit),
+// u = clamp(up, -limit, limit) (limit <= 0: no clamping).  sharpness 1, no limit and offset 0
+// give silu(gate) * up.
+template <typename T>
+__global__ void glu_mul_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restrict__ out, int rows, int width,
+                               int in_stride, float limit, float sharpness, float up_offset) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  const size_t n = (size_t)rows * width;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / width), c = (int)(i % width);
+    float g = to_float(gate[(size_t)r * in_stride + c]);
+    float u = to_float(up[(size_t)r * in_stride + c]);
+    if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
+    out[i] = from_float<T>(g * sigmoid_stable(sharpness * g) * (u + up_offset));
+  }
+}
+
+ILB_EXPORT int ilb_glu_mul(const void* in, void* out, int dtype, int rows, int width, int in_stride, float limit,
+                           float sharpness, float up_offset, cudaStream_t stream) {
+  ILB_REQUIRE(rows >= 0 && width > 0 && in_stride >= 2 * width, "glu_mul: bad sizes");
+  if (rows == 0) return 0;
+  const int threads = 256;
+  const size_t n = (size_t)rows * width;
+  const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
+  if (dtype == kF32)
+    ilb::launch(glu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)in, (const float*)in + width, (float*)out,
+                rows, width, in_stride, limit, sharpness, up_offset);
+  else if (dtype == kBF16)
+    ilb::launch(glu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)in,
+                (const __nv_bfloat16*)in + width, (__nv_bfloat16*)out, rows, width, in_stride, limit, sharpness, up_offset);
+  else
+    return fail("glu_mul: unknown dtype %d", dtype);
+  return check_launch("glu_mul");
+}
+
+// ---------------------------------------------------------------- embedding with a hashed table of token pairs
+// x[t] = table[tok_t] + pairs[r_t]; r_t = (prev_t * mul_prev + tok_t * mul_cur) mod buckets, and the
+// table's last row (number `buckets`) for a sequence's first token.  prev_t is the token before t: the
+// step's own, or, for the first token a step brings, the one kept in the request's state slot.  Then,
+// with a norm weight, x / sqrt(mean(x^2) + eps) * w.  The row goes to the residual stream and, if asked,
+// to a second buffer that later blocks read.  One block per token.
+template <typename TT>
+__global__ void __launch_bounds__(256)
+embed_pairs_kernel(const int* __restrict__ tokens, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                   const int* __restrict__ cu_q, const int* __restrict__ slots, const TT* __restrict__ table,
+                   const TT* __restrict__ pairs, int buckets, int mul_prev, int mul_cur, const int* __restrict__ prev_state,
+                   const float* __restrict__ norm_w, float eps, float* __restrict__ out, float* __restrict__ keep, int hidden,
+                   int vocab) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  __shared__ float scratch[33];
+  extern __shared__ float row[];
+  const int t = blockIdx.x;
+  const int tok = tokens[t];
+  const bool ok = tok >= 0 && tok < vocab;
+  const TT* e = table + (size_t)(ok ? tok : 0) * hidden;
+  const TT* b = nullptr;
+  if (buckets > 0) {
+    long long r = buckets;
+    if (positions[t] > 0) {
+      const int seq = seq_of_token[t];
+      int prev = 0;
+      if (t > cu_q[seq]) prev = tokens[t - 1];
+      else if (slots[seq] >= 0 && prev_state != nullptr) prev = prev_state[slots[seq]];
+      r = ((long long)prev * mul_prev + (long long)tok * mul_cur) % buckets;
+      if (r < 0) r += buckets;
+    }
+    b = pairs + (size_t)r * hidden;
+  }
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = ok ? to_float(e[i]) + (b != nullptr ? to_float(b[i]) : 0.f) : 0.f;
+    row[i] = v;
+    ss = fmaf(v, v, ss);
+  }
+  float inv = 1.f;
+  if (norm_w != nullptr) {
+    ss = block_sum(ss, scratch);
+    inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  }
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = norm_w != nullptr ? row[i] * inv * norm_w[i] : row[i];
+    out[(size_t)t * hidden + i] = v;
+    if (keep != nullptr) keep[(size_t)t * hidden + i] = v;
+  }
+}
+
+ILB_EXPORT int ilb_embed_pairs(const int* tokens, const int* positions, const int* seq_of_token, const int* cu_q, const int* slots,
+                               const void* table, const void* pairs, int dtype, int buckets, int mul_prev, int mul_cur,
+                               const int* prev_state, const float* norm_w, float eps, float* out, float* keep, int n_tokens,
+                               int hidden, int vocab, cudaStream_t stream) {
+  ILB_REQUIRE(n_tokens >= 0 && hidden > 0 && vocab > 0 && buckets >= 0, "embed_pairs: bad sizes");
+  ILB_REQUIRE(buckets == 0 || pairs != nullptr, "embed_pairs: a table of pairs is needed");
+  ILB_REQUIRE(norm_w == nullptr || eps > 0.f, "embed_pairs: eps must be positive");
+  ILB_REQUIRE((size_t)hidden * 4 <= 48 * 1024, "embed_pairs: width %d exceeds %d", hidden, 12 * 1024);
+  if (n_tokens == 0) return 0;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  const size_t smem = (size_t)hidden * 4;
+  if (dtype == kF32)
+    ilb::launch(embed_pairs_kernel<float>, dim3(n_tokens), dim3(threads), smem, stream, tokens, positions, seq_of_token, cu_q, slots,
+                (const float*)table, (const float*)pairs, buckets, mul_prev, mul_cur, prev_state, norm_w, eps, out, keep, hidden, vocab);
+  else if (dtype == kBF16)
+    ilb::launch(embed_pairs_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), smem, stream, tokens, positions, seq_of_token, cu_q,
+                slots, (const __nv_bfloat16*)table, (const __nv_bfloat16*)pairs, buckets, mul_prev, mul_cur, prev_state, norm_w, eps, out,
+                keep, hidden, vocab);
+  else
+    return fail("embed_pairs: unknown dtype %d", dtype);
+  return check_launch("embed_pairs");
+}
+
+// prev_state[slot of sequence s] = the last token sequence s brings in this step.  A launch of its own,
+// after the embedding has read the old values.
+__global__ void store_last_tokens_kernel(const int* __restrict__ tokens, const int* __restrict__ cu_q,
+                                         const int* __restrict__ slots, int* __restrict__ prev_state, int n_seqs) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  const int s = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= n_seqs) return;
+  const int slot = slots[s], last = cu_q[s + 1] - 1;
+  if (slot >= 0 && last >= cu_q[s]) prev_state[slot] = tokens[last];
+}
+
+ILB_EXPORT int ilb_store_last_tokens(const int* tokens, const int* cu_q, const int* slots, int* prev_state, int n_seqs,
+                                     cudaStream_t stream) {
+  ILB_REQUIRE(n_seqs >= 0, "store_last_tokens: bad sizes");
+  if (n_seqs == 0) return 0;
+  ilb::launch(store_last_tokens_kernel, dim3((n_seqs + 127) / 128), dim3(128), 0, stream, tokens, cu_q, slots, prev_state, n_seqs);
+  return check_launch("store_last_tokens");
+}
+
+// ---------------------------------------------------------------- two 32-bit rows side by side, in another type
+template <typename TO>
+__global__ void concat_cast_kernel(const float* __restrict__ a, const float* __restrict__ b, TO* __restrict__ out, int rows, int width) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  const size_t n = (size_t)rows * width;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / width, c = i % width;
+    out[r * 2 * width + c] = from_float<TO>(a[i]);
+    out[r * 2 * width + width + c] = from_float<TO>(b[i]);
+  }
+}
+
+// out[r] = [a[r], b[r]]: a, b [rows, width] 32-bit, out [rows, 2 * width] of `out_dtype`.
+ILB_EXPORT int ilb_concat_cast(const float* a, const float* b, void* out, int out_dtype, int rows, int width, cudaStream_t stream) {
+  ILB_REQUIRE(rows >= 0 && width > 0, "concat_cast: bad sizes");
+  if (rows == 0) return 0;
+  const size_t n = (size_t)rows * width;
+  const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  if (out_dtype == kF32) ilb::launch(concat_cast_kernel<float>, dim3(blocks), dim3(256), 0, stream, a, b, (float*)out, rows, width);
+  else if (out_dtype == kBF16) ilb::launch(concat_cast_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, a, b, (__nv_bfloat16*)out, rows, width);
+  else return fail("concat_cast: unknown dtype %d", out_dtype);
+  return check_launch("concat_cast");
+}
+
 ILB_DEFINE_LAST_ERROR()

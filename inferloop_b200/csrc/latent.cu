@@ -1,0 +1,113 @@
+// Attention over a cached low-rank latent: what lies around the attention kernel itself.
+//
+// A token caches one vector c = rms(W_dkv h) * g of `rank` elements; head i's keys and values are
+// k = Uk_i c and v = Uv_i c.  Nothing but c is stored: the score q_i . k = (Uk_i^T q_i) . c, and the
+// weighted sum of values is Uv_i (sum_j p_j c_j), so the attention kernels run with one shared
+// "kv head" whose keys and values are both the cached latents, on queries mapped by Uk^T, and
+// their output is mapped by Uv afterwards.
+//
+//   latent_write   c = x / sqrt(mean(x^2) + eps) * g in 32-bit from the projection's columns, stored
+//                  into the token's place of its page (dummy rows and released pages are skipped)
+//   head_matmul    out[t, i, :] = x[t, i, :] W[i] for every head i, W [heads, K, N]: the two maps
+//                  above, 16 tokens a block so that a head's matrix is read once per 16 tokens;
+//                  32-bit sums over k in order
+#include <math.h>
+#include "common.cuh"
+
+using namespace ilb;
+
+template <typename TI, typename TC>
+__global__ void __launch_bounds__(128)
+latent_write_kernel(const TI* __restrict__ proj, int ld, int col0, int rank, const float* __restrict__ w, float eps,
+                    const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                    const int* __restrict__ block_table, int max_blocks, int page_size, int num_pages, TC* __restrict__ cache) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  const TI* row = proj + (size_t)t * ld + col0;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) {
+    const float v = to_float(row[i]);
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)rank + eps);
+  const int pos = positions[t];
+  const int page = block_table[(size_t)seq_of_token[t] * max_blocks + pos / page_size];
+  if (page < 0 || page >= num_pages) return;
+  TC* dst = cache + ((size_t)page * page_size + pos % page_size) * rank;
+  for (int i = threadIdx.x; i < rank; i += blockDim.x)
+    dst[i] = from_float<TC>(to_float(row[i]) * inv * w[i]);
+}
+
+ILB_EXPORT int ilb_latent_write(const void* proj, int dtype, int ld, int col0, int rank, const float* w, float eps,
+                                const int* positions, const int* seq_of_token, const int* block_table, int max_blocks,
+                                int page_size, int num_pages, void* cache, int cache_dtype, int n_tokens, cudaStream_t stream) {
+  ILB_REQUIRE(rank > 0 && ld >= col0 + rank && n_tokens >= 0 && eps > 0.f, "latent_write: bad sizes");
+  ILB_REQUIRE(page_size > 0 && max_blocks > 0 && num_pages > 0, "latent_write: bad cache geometry");
+  if (n_tokens == 0) return 0;
+#define ILB_LW(TI, TC) ilb::launch(latent_write_kernel<TI, TC>, dim3(n_tokens), dim3(128), 0, stream, (const TI*)proj, ld, col0, rank, w, \
+                                    eps, positions, seq_of_token, block_table, max_blocks, page_size, num_pages, (TC*)cache)
+  if (dtype == kF32 && cache_dtype == kF32) ILB_LW(float, float);
+  else if (dtype == kBF16 && cache_dtype == kBF16) ILB_LW(__nv_bfloat16, __nv_bfloat16);
+  else if (dtype == kBF16 && cache_dtype == kF32) ILB_LW(__nv_bfloat16, float);
+  else if (dtype == kF32 && cache_dtype == kBF16) ILB_LW(float, __nv_bfloat16);
+  else return fail("latent_write: unsupported dtypes %d/%d", dtype, cache_dtype);
+#undef ILB_LW
+  return check_launch("latent_write");
+}
+
+constexpr int kHeadTokens = 16;
+
+template <typename TI, typename TW, typename TO>
+__global__ void __launch_bounds__(128)
+head_matmul_kernel(const TI* __restrict__ x, int ldx, const TW* __restrict__ w, TO* __restrict__ out, int ldo,
+                   int n_tokens, int K, int N) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  extern __shared__ __align__(16) float xs[];           // [kHeadTokens][K]
+  const int t0 = blockIdx.x * kHeadTokens, h = blockIdx.y;
+  const int ts = min(kHeadTokens, n_tokens - t0);
+  for (int i = threadIdx.x; i < kHeadTokens * K; i += blockDim.x) {
+    const int tt = i / K, k = i % K;
+    xs[i] = tt < ts ? to_float(x[(size_t)(t0 + tt) * ldx + (size_t)h * K + k]) : 0.f;
+  }
+  __syncthreads();
+  const int n = blockIdx.z * 128 + threadIdx.x;
+  if (n >= N) return;
+  float acc[kHeadTokens];
+#pragma unroll
+  for (int tt = 0; tt < kHeadTokens; ++tt) acc[tt] = 0.f;
+  const TW* wp = w + (size_t)h * K * N + n;
+  for (int k = 0; k < K; ++k) {
+    const float wv = to_float(wp[(size_t)k * N]);
+#pragma unroll
+    for (int tt = 0; tt < kHeadTokens; ++tt) acc[tt] = fmaf(xs[tt * K + k], wv, acc[tt]);
+  }
+#pragma unroll
+  for (int tt = 0; tt < kHeadTokens; ++tt)
+    if (tt < ts) out[(size_t)(t0 + tt) * ldo + (size_t)h * N + n] = from_float<TO>(acc[tt]);
+}
+
+// x: [T, ldx] of `dtype`, head i at columns i * K ..; w: [heads, K, N] of `dtype`; out: [T, ldo] of
+// `out_dtype`, head i at columns i * N ...
+ILB_EXPORT int ilb_head_matmul(const void* x, int dtype, int ldx, const void* w, void* out, int out_dtype, int ldo,
+                               int n_tokens, int heads, int K, int N, cudaStream_t stream) {
+  ILB_REQUIRE(n_tokens >= 0 && heads > 0 && heads <= 65535 && K > 0 && N > 0, "head_matmul: bad sizes");
+  ILB_REQUIRE(ldx >= heads * K && ldo >= heads * N, "head_matmul: strides too small");
+  const size_t smem = sizeof(float) * kHeadTokens * K;
+  ILB_REQUIRE(smem <= 48 * 1024, "head_matmul: inner size %d exceeds %d", K, 48 * 1024 / 4 / kHeadTokens);
+  if (n_tokens == 0) return 0;
+  const dim3 grid((n_tokens + kHeadTokens - 1) / kHeadTokens, heads, (N + 127) / 128);
+#define ILB_HM(TI, TO) ilb::launch(head_matmul_kernel<TI, TI, TO>, grid, dim3(128), smem, stream, (const TI*)x, ldx, (const TI*)w, \
+                                    (TO*)out, ldo, n_tokens, K, N)
+  if (dtype == kF32 && out_dtype == kF32) ILB_HM(float, float);
+  else if (dtype == kBF16 && out_dtype == kBF16) ILB_HM(__nv_bfloat16, __nv_bfloat16);
+  else if (dtype == kBF16 && out_dtype == kF32) ILB_HM(__nv_bfloat16, float);
+  else return fail("head_matmul: unsupported dtypes %d/%d", dtype, out_dtype);
+#undef ILB_HM
+  return check_launch("head_matmul");
+}
+
+ILB_DEFINE_LAST_ERROR()

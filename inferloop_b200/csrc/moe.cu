@@ -129,8 +129,8 @@ ILB_EXPORT int ilb_moe_logits(const void* x, const void* w, int dtype, float* ou
 
 // One warp per token.
 __global__ void __launch_bounds__(128)
-moe_route_kernel(const float* __restrict__ logits, int ld, int n_tokens, int experts, int top, int softmax,
-                 int renormalize, int* __restrict__ choice, float* __restrict__ weight) {
+moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int ld, int n_tokens, int experts, int top,
+                 int softmax, int renormalize, int* __restrict__ choice, float* __restrict__ weight) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -142,7 +142,7 @@ moe_route_kernel(const float* __restrict__ logits, int ld, int n_tokens, int exp
 #pragma unroll
   for (int i = 0; i < kMaxExpertsPerLane; ++i) {
     const int e = lane + 32 * i;
-    s[i] = e < experts ? z[e] : -INFINITY;
+    s[i] = e < experts ? (bias != nullptr ? z[e] + bias[e] : z[e]) : -INFINITY;
     zmax = fmaxf(zmax, s[i]);
   }
   if (softmax) {
@@ -196,14 +196,15 @@ ILB_EXPORT int ilb_moe_max_experts() { return 32 * kMaxExpertsPerLane; }
 ILB_EXPORT int ilb_moe_max_top() { return kMaxTop; }
 
 // logits: [T, ld] 32-bit, the first `experts` columns are the router's.  choice / weight: [T, top].
-ILB_EXPORT int ilb_moe_route(const float* logits, int ld, int n_tokens, int experts, int top, int softmax, int renormalize,
-                             int* choice, float* weight, cudaStream_t stream) {
+// bias: [experts] added to the logits first, or null.
+ILB_EXPORT int ilb_moe_route(const float* logits, const float* bias, int ld, int n_tokens, int experts, int top, int softmax,
+                             int renormalize, int* choice, float* weight, cudaStream_t stream) {
   ILB_REQUIRE(n_tokens >= 0 && experts > 0 && experts <= 32 * kMaxExpertsPerLane, "moe_route: %d experts (at most %d)", experts,
               32 * kMaxExpertsPerLane);
   ILB_REQUIRE(top > 0 && top <= experts && top <= kMaxTop, "moe_route: top %d of %d experts (at most %d)", top, experts, kMaxTop);
   ILB_REQUIRE(ld >= experts, "moe_route: row stride too small");
   if (n_tokens == 0) return 0;
-  ilb::launch(moe_route_kernel, dim3((n_tokens + 3) / 4), dim3(128), 0, stream, logits, ld, n_tokens, experts, top, softmax,
+  ilb::launch(moe_route_kernel, dim3((n_tokens + 3) / 4), dim3(128), 0, stream, logits, bias, ld, n_tokens, experts, top, softmax,
               renormalize, choice, weight);
   return check_launch("moe_route");
 }

@@ -37,7 +37,6 @@ constexpr uint32_t kBytesA = kRows * kBlockK * 2;
 template <int MS, int BN> __host__ __device__ constexpr uint32_t stage_bytes() { return MS * kBytesA + BN * kBlockK * 2; }
 template <int MS, int BN, int kStages> constexpr size_t smem_bytes() { return (size_t)kStages * stage_bytes<MS, BN>() + 1024 + (2 * kStages + 4) * 8; }
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
 // K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
@@ -54,7 +53,15 @@ struct Params {
   int* error_flag;
   int N, K, ldo, k_blocks;
   int swiglu, out_f32;
+  // the gated unit of the epilogue: a(g) * (u + act_offset), a(g) = g * sigmoid(act_sharp * g), with g = min(gate, act_limit)
+  // and u = clamp(up, -act_limit, act_limit) when act_limit > 0 (sharpness 1, no limit, offset 0: silu(gate) * up)
+  float act_limit, act_sharp, act_offset;
 };
+
+__device__ __forceinline__ float glu_mul(const Params& p, float g, float u) {
+  if (p.act_limit > 0.f) { g = fminf(g, p.act_limit); u = fminf(fmaxf(u, -p.act_limit), p.act_limit); }
+  return __fdividef(g, 1.0f + __expf(-p.act_sharp * g)) * (u + p.act_offset);
+}
 
 // 32 consecutive columns of one output row, from column c on; columns from `limit` on are not written.
 __device__ __forceinline__ void store32(const Params& p, size_t out_row, int c, int limit, const float (&v)[32]) {
@@ -179,7 +186,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               tmem_load_32(taddr + pair * 128 + 64 + 32 * half, up);
               float v[32];
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = silu_mul(gt[j], up[j]);
+              for (int j = 0; j < 32; ++j) v[j] = glu_mul(p, gt[j], up[j]);
               store32(p, out_row, c, p.N / 2, v);
             }
           }
@@ -324,7 +331,7 @@ moe_gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
             tmem_load_32(taddr + pair * 128 + 64 + 32 * half, up);
             float v[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = silu_mul(gt[i], up[i]);
+            for (int i = 0; i < 32; ++i) v[i] = glu_mul(p, gt[i], up[i]);
             store32(p, out_row, c, p.N / 2, v);
           }
         }
@@ -435,7 +442,7 @@ ILB_EXPORT int ilb_moe_gemm_tc_supported(int N, int K, int lda, int swiglu) {
 // asks for the persistent form of the 128 x 256 tile.
 ILB_EXPORT int ilb_moe_gemm_tc(const void* A, const void* W, void* out, int out_f32, int rows, int groups, int N, int K, int lda,
                                int ldo, int swiglu, const int* block_group, int block_rows, int tile_n, int* error_flag,
-                               cudaStream_t stream) {
+                               float act_limit, float act_sharp, float act_offset, cudaStream_t stream) {
   ILB_REQUIRE(rows >= 0 && groups > 0 && N > 0 && K > 0, "moe_gemm: bad sizes rows=%d groups=%d N=%d K=%d", rows, groups, N, K);
   ILB_REQUIRE(block_rows == 128 || block_rows == 256, "moe_gemm: blocks of 128 or 256 rows, not %d", block_rows);
   ILB_REQUIRE(tile_n == 256 || ((tile_n == 128 || tile_n == 257) && block_rows == 128), "moe_gemm: tiles of %d x %d are not built", block_rows, tile_n);
@@ -451,6 +458,7 @@ ILB_EXPORT int ilb_moe_gemm_tc(const void* A, const void* W, void* out, int out_
   p.out = out; p.block_group = block_group; p.error_flag = error_flag;
   p.N = N; p.K = K; p.ldo = ldo; p.k_blocks = (K + kBlockK - 1) / kBlockK;
   p.swiglu = swiglu ? 1 : 0; p.out_f32 = out_f32 ? 1 : 0;
+  p.act_limit = act_limit; p.act_sharp = act_sharp; p.act_offset = act_offset;
   if (block_rows == 256) return launch_tiles<2, 256, 3>(A, W, p, rows, groups, lda, stream);
   if (tile_n == 257) return launch_persistent<256, 4>(A, W, p, rows, groups, lda, stream);
   if (tile_n == 256) return launch_tiles<1, 256, 4>(A, W, p, rows, groups, lda, stream);

@@ -125,6 +125,136 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
           _i(width), _i(gate_up.shape[1]), _stream(out))
 
 
+def glu_mul(gate_up: torch.Tensor, out: torch.Tensor, limit: float = 0.0, sharpness: float = 1.0, up_offset: float = 0.0) -> None:
+    """out = g * sigmoid(sharpness * g) * (u + up_offset) with g = min(gate, limit), u = clamp(up, -limit, limit)
+    (limit 0: no clamping); gate = gate_up[:, :I], up = gate_up[:, I:2I]."""
+    _need(gate_up, "glu_mul in"); _need(out, "glu_mul out", gate_up.dtype)
+    rows, width = out.shape
+    if gate_up.shape[0] != rows or gate_up.shape[1] != 2 * width:
+        raise KernelError("glu_mul: shapes do not agree")
+    _call("elementwise", "ilb_glu_mul", _ptr(gate_up), _ptr(out), _i(_code(out)), _i(rows), _i(width), _i(gate_up.shape[1]),
+          _f(limit), _f(sharpness), _f(up_offset), _stream(out))
+
+
+def embed_pairs(step, table: torch.Tensor, pairs: Optional[torch.Tensor], buckets: int, mul_prev: int, mul_cur: int,
+                prev_state: Optional[torch.Tensor], norm_weight: Optional[torch.Tensor], eps: float, out: torch.Tensor,
+                keep: Optional[torch.Tensor] = None) -> None:
+    """out[t] = norm(table[token] + pairs[(previous token * mul_prev + token * mul_cur) mod buckets]) (the last row
+    of `pairs` for a sequence's first token); the token before a step's first one comes from `prev_state`
+    [slots] int32.  `keep`, if given, receives the same rows.  See elementwise.cu."""
+    _need(table, "embed table"); _need(pairs, "pair table", table.dtype); _need(prev_state, "previous tokens", torch.int32)
+    _need(norm_weight, "embed norm weight", torch.float32); _need(out, "embed out", torch.float32); _need(keep, "embed keep", torch.float32)
+    T, H = out.shape
+    if table.shape[1] != H or (pairs is not None and tuple(pairs.shape) != (buckets + 1, H)) or (keep is not None and keep.shape != out.shape):
+        raise KernelError("embed_pairs: shapes do not agree")
+    _call("elementwise", "ilb_embed_pairs", _ptr(step.tokens), _ptr(step.positions), _ptr(step.seq_of_token), _ptr(step.cu_q),
+          _ptr(step.slots), _ptr(table), _ptr(pairs), _i(_code(table)), _i(buckets if pairs is not None else 0), _i(mul_prev), _i(mul_cur),
+          _ptr(prev_state), _ptr(norm_weight), _f(eps), _ptr(out), _ptr(keep), _i(T), _i(H), _i(table.shape[0]), _stream(out))
+
+
+def store_last_tokens(step, prev_state: torch.Tensor) -> None:
+    """prev_state[slot] = the last token each sequence brings in this step."""
+    _need(prev_state, "previous tokens", torch.int32)
+    _call("elementwise", "ilb_store_last_tokens", _ptr(step.tokens), _ptr(step.cu_q), _ptr(step.slots), _ptr(prev_state),
+          _i(step.n_seqs), _stream(prev_state))
+
+
+def concat_cast(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = [a[r], b[r]] of two 32-bit matrices, in out's dtype."""
+    _need(a, "concat a", torch.float32); _need(b, "concat b", torch.float32); _need(out, "concat out")
+    rows, width = a.shape
+    if b.shape != a.shape or tuple(out.shape) != (rows, 2 * width):
+        raise KernelError("concat_cast: shapes do not agree")
+    _call("elementwise", "ilb_concat_cast", _ptr(a), _ptr(b), _ptr(out), _i(_code(out)), _i(rows), _i(width), _stream(out))
+
+
+# --------------------------------------------------------------------------- state-space recurrence
+SSM_CONV_TILE = 16         # tokens of a sequence per block of the convolution
+SSM_CHUNK = 64             # tokens per chunk when a long portion's recurrence runs chunks side by side
+SSM_CHUNK_FROM = 128       # portions from this many tokens on are cut into chunks
+
+
+def ssm_conv(proj: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, bias: torch.Tensor, state: torch.Tensor,
+             step, out: torch.Tensor) -> None:
+    """out[t, c] = silu(bias[c] + sum_k weight[c, k] * raw[t - (taps - 1) + k, c]) over columns col0 .. of `proj`; the raw
+    inputs ahead of the step come from state [slots, taps - 1, channels], which is brought up to date."""
+    _need(proj, "ssm projection"); _need(weight, "conv weight", torch.float32); _need(bias, "conv bias", torch.float32)
+    _need(state, "conv state", torch.float32); _need(out, "conv out", torch.float32)
+    T, taps = proj.shape[0], weight.shape[1]
+    if tuple(weight.shape) != (channels, taps) or bias.numel() != channels or tuple(out.shape) != (T, channels) \
+            or tuple(state.shape[1:]) != (max(taps - 1, 0), channels):
+        raise KernelError("ssm_conv: shapes do not agree")
+    n_tiles = sum(-(-n // SSM_CONV_TILE) for n in step.h_q_len) + (step.n_seqs - len(step.h_q_len))
+    _call("ssm", "ilb_ssm_conv", _ptr(proj), _i(_code(proj)), _i(proj.stride(0)), _i(col0), _i(channels), _i(taps), _ptr(weight),
+          _ptr(bias), _ptr(state), _ptr(step.cu_q), _ptr(step.slots), _i(step.n_seqs), _i(n_tiles), _ptr(out), _stream(out))
+
+
+def ssm_scan(act: torch.Tensor, proj: torch.Tensor, dt_col0: int, dt_bias: torch.Tensor, a_log: torch.Tensor, skip: torch.Tensor,
+             state: torch.Tensor, y: torch.Tensor, step, heads: int, head_dim: int, n_state: int, groups: int,
+             workspace=None, chunk: Optional[int] = None) -> None:
+    """The recurrence S_t = exp(-exp(a_log) d_t) S_{t-1} + d_t B_t u_t^T, y_t = S_t^T C_t + skip * u_t per head over the
+    step's tokens, from and to state [slots, heads, n_state, head_dim] (see ssm.cu).  `chunk`: None picks by the
+    longest portion; 0 runs every sequence in one go; n cuts portions into chunks of n tokens."""
+    _need(act, "ssm activations", torch.float32); _need(proj, "ssm projection"); _need(state, "ssm state", torch.float32)
+    _need(y, "ssm y", torch.float32)
+    for t, w in ((dt_bias, "dt bias"), (a_log, "decay logarithms"), (skip, "skip weights")):
+        _need(t, "ssm " + w, torch.float32)
+        if t.numel() != heads:
+            raise KernelError("ssm_scan: one " + w + " per head")
+    T, channels = act.shape
+    if channels != heads * head_dim + 2 * groups * n_state or tuple(y.shape) != (T, heads * head_dim) \
+            or tuple(state.shape[1:]) != (heads, n_state, head_dim):
+        raise KernelError("ssm_scan: shapes do not agree")
+    if chunk is None:
+        chunk = SSM_CHUNK if step.max_q_len >= SSM_CHUNK_FROM else 0
+    chunk_state = chunk_decay = None
+    n_blocks = step.n_seqs
+    if chunk:
+        if workspace is None:
+            raise KernelError("ssm_scan: chunks need a workspace")
+        n_blocks = sum(-(-n // chunk) for n in step.h_q_len) + (step.n_seqs - len(step.h_q_len))
+        chunk_state = workspace.buffer("ssm.chunk_state", (n_blocks, heads, n_state, head_dim), torch.float32)
+        chunk_decay = workspace.buffer("ssm.chunk_decay", (n_blocks, heads), torch.float32)
+    _call("ssm", "ilb_ssm_scan", _ptr(act), _ptr(proj), _i(_code(proj)), _i(proj.stride(0)), _i(dt_col0), _i(channels), _ptr(dt_bias),
+          _ptr(a_log), _ptr(skip), _ptr(state), _ptr(chunk_state), _ptr(chunk_decay), _ptr(y), _ptr(step.cu_q), _ptr(step.slots),
+          _i(step.n_seqs), _i(heads), _i(head_dim), _i(n_state), _i(groups), _i(chunk), _i(n_blocks), _stream(y))
+
+
+def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, groups: int, out: torch.Tensor) -> None:
+    """out = rms over each of `groups` equal parts of (y * silu(gate[:, :width])) * weight; y is 32-bit."""
+    _need(y, "gated norm y", torch.float32); _need(gate, "gated norm gate", contiguous=False); _need(weight, "gated norm weight", torch.float32)
+    _need(out, "gated norm out", gate.dtype)
+    T, width = y.shape
+    if gate.shape[0] != T or gate.shape[1] < width or gate.stride(1) != 1 or weight.numel() != width or out.shape != y.shape or width % groups:
+        raise KernelError("gated_group_norm: shapes do not agree")
+    _call("ssm", "ilb_gated_group_norm", _ptr(y), _ptr(gate), _i(_code(gate)), _i(gate.stride(0)), _ptr(weight), _ptr(out), _i(T), _i(width),
+          _i(groups), _f(eps), _stream(out))
+
+
+# --------------------------------------------------------------------------- attention over a cached latent
+def latent_write(proj: torch.Tensor, col0: int, rank: int, weight: torch.Tensor, eps: float, step, block_table: torch.Tensor,
+                 cache: torch.Tensor) -> None:
+    """cache[page of t, place of t] = rms(proj[t, col0 : col0 + rank]) * weight; cache is [pages, 1, page_size, rank]."""
+    _need(proj, "latent projection"); _need(weight, "latent norm weight", torch.float32); _need(cache, "latent cache")
+    _need(block_table, "block table", torch.int32)
+    if cache.dim() != 4 or cache.shape[1] != 1 or cache.shape[3] != rank or weight.numel() != rank:
+        raise KernelError("latent_write: cache must be [pages, 1, page_size, rank]")
+    _call("latent", "ilb_latent_write", _ptr(proj), _i(_code(proj)), _i(proj.stride(0)), _i(col0), _i(rank), _ptr(weight), _f(eps),
+          _ptr(step.positions), _ptr(step.seq_of_token), _ptr(block_table), _i(block_table.shape[1]), _i(cache.shape[2]),
+          _i(cache.shape[0]), _ptr(cache), _i(_code(cache)), _i(proj.shape[0]), _stream(cache))
+
+
+def head_matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i, :] = x[t, i, :] @ w[i] for every head i; x [T, >= heads * K] (row stride free), w [heads, K, N],
+    out [T, heads * N]."""
+    _need(x, "head_matmul x", contiguous=False); _need(w, "head_matmul w", x.dtype); _need(out, "head_matmul out")
+    heads, K, N = w.shape
+    if x.stride(1) != 1 or x.shape[1] < heads * K or tuple(out.shape) != (x.shape[0], heads * N):
+        raise KernelError("head_matmul: shapes do not agree")
+    _call("latent", "ilb_head_matmul", _ptr(x), _i(_code(x)), _i(x.stride(0)), _ptr(w), _ptr(out), _i(_code(out)), _i(out.stride(0)),
+          _i(x.shape[0]), _i(heads), _i(K), _i(N), _stream(out))
+
+
 def gather_rows(x: torch.Tensor, index: torch.Tensor, out: torch.Tensor, streams: int = 1) -> None:
     """out[r, :] = the sum of the `streams` copies of row index[r] of x [rows, streams * width]."""
     _need(x, "gather x", torch.float32); _need(index, "gather index", torch.int32); _need(out, "gather out", torch.float32)
@@ -188,12 +318,15 @@ def moe_logits(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 
 
 def moe_route(logits: torch.Tensor, experts: int, top: int, softmax: bool, renormalize: bool,
-              choice: torch.Tensor, weight: torch.Tensor) -> None:
+              choice: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
+    """The `top` experts with the largest scores of every token and their weights; `bias` [experts]
+    is added to the logits first."""
     _need(logits, "router logits", torch.float32); _need(choice, "moe choice", torch.int32); _need(weight, "moe weight", torch.float32)
+    _need(bias, "router bias", torch.float32)
     T = logits.shape[0]
-    if choice.numel() != T * top or weight.numel() != T * top or logits.shape[1] < experts:
+    if choice.numel() != T * top or weight.numel() != T * top or logits.shape[1] < experts or (bias is not None and bias.numel() != experts):
         raise KernelError("moe_route: shapes do not agree")
-    _call("moe", "ilb_moe_route", _ptr(logits), _i(logits.stride(0)), _i(T), _i(experts), _i(top), _i(1 if softmax else 0),
+    _call("moe", "ilb_moe_route", _ptr(logits), _ptr(bias), _i(logits.stride(0)), _i(T), _i(experts), _i(top), _i(1 if softmax else 0),
           _i(1 if renormalize else 0), _ptr(choice), _ptr(weight), _stream(logits))
 
 
@@ -256,10 +389,11 @@ MOE_TILE_N = 0             # tests and measurements force 128, 256 or 257 (256 w
 
 
 def moe_gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, block_group: torch.Tensor, swiglu: bool = False,
-                block_rows: int = GROUP_ROWS_TC, tile_n: int = 0) -> None:
+                block_rows: int = GROUP_ROWS_TC, tile_n: int = 0, act: tuple = (0.0, 1.0, 0.0)) -> None:
     """out[rows of block b] = a[rows of block b] @ w[block_group[b]].T on tcgen05 tensor cores for
     blocks of 128 or 256 rows (moe_gemm_tcgen05.cu); with `swiglu`, w holds blocks of 64 gate rows
-    followed by their 64 up rows and out is [rows, N / 2] = silu(gate) * up."""
+    followed by their 64 up rows and out is [rows, N / 2] = silu(gate) * up; or, with `act` = (limit, sharpness, up_offset), the gated
+    unit of `glu_mul`."""
     _need(a, "moe gemm a", torch.bfloat16); _need(w, "moe gemm w", torch.bfloat16); _need(out, "moe gemm out")
     _need(block_group, "moe gemm groups", torch.int32)
     M, K = a.shape
@@ -277,7 +411,7 @@ def moe_gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, block_group
     st = _tc_state(a.device)
     _call("moe_gemm_tcgen05", "ilb_moe_gemm_tc", _ptr(a), _ptr(w), _ptr(out), _i(1 if out.dtype == torch.float32 else 0), _i(M),
           _i(w.shape[0]), _i(N), _i(K), _i(a.stride(0)), _i(out.stride(0)), _i(1 if swiglu else 0), _ptr(block_group),
-          _i(block_rows), _i(tile_n), _ptr(st.error), _stream(out))
+          _i(block_rows), _i(tile_n), _ptr(st.error), _f(act[0]), _f(act[1]), _f(act[2]), _stream(out))
 
 
 def gemm_simt_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, block_group: torch.Tensor) -> None:
@@ -390,9 +524,12 @@ def qk_norm_rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optiona
 def paged_attention_simple(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
                            v_cache: torch.Tensor, positions: torch.Tensor,
                            seq_of_token: torch.Tensor, block_table: torch.Tensor, window: int,
-                           scale: float, nq: int, nkv: int, d: int, dv: Optional[int] = None) -> None:
+                           scale: float, nq: int, nkv: int, d: int, dv: Optional[int] = None,
+                           sink: Optional[torch.Tensor] = None) -> None:
     dv = d if dv is None else int(dv)
-    _need(q, "attention q"); _need(out, "attention out", q.dtype)
+    _need(q, "attention q"); _need(out, "attention out", q.dtype); _need(sink, "attention sink", torch.float32)
+    if sink is not None and sink.numel() != nq:
+        raise KernelError("attention: one sink logit per query head")
     _need(k_cache, "k cache"); _need(v_cache, "v cache", k_cache.dtype)
     _need(positions, "positions", torch.int32); _need(seq_of_token, "seq_of_token", torch.int32)
     _need(block_table, "block table", torch.int32)
@@ -403,7 +540,7 @@ def paged_attention_simple(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Te
           _ptr(k_cache), _ptr(v_cache), _i(_code(k_cache)), _ptr(positions), _ptr(seq_of_token),
           _ptr(block_table), _i(block_table.shape[1]), _i(page_size), _i(num_pages),
           _i(window or 0), _f(scale), _i(q.shape[0]), _i(nq), _i(nkv), _i(d), _i(dv), _i(q.shape[1]),
-          _i(out.shape[1]), _stream(q))
+          _i(out.shape[1]), _ptr(sink), _stream(q))
 
 
 # --------------------------------------------------------------------------- sampling
@@ -623,18 +760,18 @@ def attention_prefill_tc(q, out, k_cache, v_cache, positions, cu_q, block_table,
 
 
 def attention_prefill(q, out, k_cache, v_cache, positions, cu_q, block_table, window, scale, n_seqs,
-                      n_tiles, nq, nkv, d) -> None:
+                      n_tiles, nq, nkv, d, sink=None) -> None:
     for t, w in ((q, "q"), (out, "out"), (k_cache, "k cache"), (v_cache, "v cache")):
         _need(t, "attention " + w, torch.bfloat16)
     num_pages, _, page_size, _ = k_cache.shape
     _call("attention_flash", "ilb_attention_prefill", _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache),
           _ptr(positions), _ptr(cu_q), _ptr(block_table), _i(block_table.shape[1]), _i(page_size),
           _i(num_pages), _i(window or 0), _f(scale), _i(n_seqs), _i(n_tiles), _i(nq), _i(nkv), _i(d),
-          _i(q.shape[1]), _i(out.shape[1]), _stream(q))
+          _i(q.shape[1]), _i(out.shape[1]), _ptr(sink), _stream(q))
 
 
 def attention_decode(q, out, k_cache, v_cache, positions, cu_q, block_table, window, scale, n_seqs,
-                     nq, nkv, d, chunk, max_chunks, scratch, tickets) -> None:
+                     nq, nkv, d, chunk, max_chunks, scratch, tickets, sink=None) -> None:
     for t, w in ((q, "q"), (out, "out"), (k_cache, "k cache"), (v_cache, "v cache")):
         _need(t, "attention " + w, torch.bfloat16)
     _need(scratch, "attention scratch", torch.float32); _need(tickets, "attention tickets", torch.int32)
@@ -643,7 +780,7 @@ def attention_decode(q, out, k_cache, v_cache, positions, cu_q, block_table, win
           _ptr(positions), _ptr(cu_q), _ptr(block_table), _i(block_table.shape[1]), _i(page_size),
           _i(num_pages), _i(window or 0), _f(scale), _i(n_seqs), _i(nq), _i(nkv), _i(d), _i(q.shape[1]),
           _i(out.shape[1]), _i(chunk), _i(max_chunks), _ptr(scratch), ctypes.c_longlong(scratch.numel()),
-          _ptr(tickets), _i(tickets.numel()), _stream(q))
+          _ptr(tickets), _i(tickets.numel()), _ptr(sink), _stream(q))
 
 
 def attention_decode_tma_supported(nq: int, nkv: int, d: int, page_size: int) -> bool:
@@ -726,19 +863,23 @@ def attention_decode_fused(qkv, out, q_weight, k_weight, eps, rope_table, k_cach
 
 def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
               step, block_table: torch.Tensor, window: int, scale: float, nq: int, nkv: int,
-              d: int, workspace=None, decode_chunk: int = DECODE_CHUNK_MIN, dv: Optional[int] = None) -> None:
+              d: int, workspace=None, decode_chunk: int = DECODE_CHUNK_MIN, dv: Optional[int] = None,
+              sink: Optional[torch.Tensor] = None) -> None:
     """Causal attention of the step's tokens over the cache; picks the kernel: the
     tensor-core kernels for a bfloat16 cache and a head size they are built for (split-KV
-    when every sequence brings one token), else the exact kernel."""
+    when every sequence brings one token), else the exact kernel.  `sink` [nq] 32-bit: a logit
+    per query head that joins the softmax's denominator (no key, no value, no scale)."""
     dv = d if dv is None else int(dv)
+    _need(sink, "attention sink", torch.float32)
     fast = (q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and attention_flash_supported(d) and dv == d
             and workspace is not None and FLASH_ENABLED)
     if not fast:          # the 32-bit path, and values of another head size than the keys'
         paged_attention_simple(q, out, k_cache, v_cache, step.positions, step.seq_of_token,
-                               block_table, window, scale, nq, nkv, d, dv)
+                               block_table, window, scale, nq, nkv, d, dv, sink)
         return
     G = nq // nkv
-    if step.decode_only and DECODE_CLUSTER_ENABLED and attention_decode_tma_supported(nq, nkv, d, k_cache.shape[2]):
+    # (the cluster-merged decode kernel and the tcgen05 prefill kernel take no sink: such layers use the mma.sync kernels)
+    if step.decode_only and DECODE_CLUSTER_ENABLED and sink is None and attention_decode_tma_supported(nq, nkv, d, k_cache.shape[2]):
         attention_decode_tma(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,
                              step.n_seqs, nq, nkv, d, getattr(step, "max_kv_len", 0) >= DECODE_LONG_CONTEXT)
     elif step.decode_only:
@@ -748,8 +889,8 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
         scratch = workspace.buffer("attn.decode_scratch", (step.n_seqs * nkv * max_chunks * G * (d + 2),), torch.float32)
         tickets = workspace.zeroed("attn.decode_tickets", (max(step.n_seqs * nkv, 4096),), torch.int32)
         attention_decode(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,
-                         step.n_seqs, nq, nkv, d, decode_chunk, max_chunks, scratch, tickets)
-    elif TC_ATTENTION_ENABLED and attention_tc_supported(nq, nkv, d, k_cache.shape[2]):
+                         step.n_seqs, nq, nkv, d, decode_chunk, max_chunks, scratch, tickets, sink)
+    elif TC_ATTENTION_ENABLED and sink is None and attention_tc_supported(nq, nkv, d, k_cache.shape[2]):
         # A mixed step: the sequences that bring one token go to the split-KV decode kernel
         # (it leaves the others alone), the portions to the prefill kernel (which leaves those).
         lens = step.h_q_len
@@ -772,7 +913,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
     else:
         n_tiles = sum(-(-n * G // 64) for n in step.h_q_len)
         attention_prefill(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,
-                          step.n_seqs, n_tiles, nq, nkv, d)
+                          step.n_seqs, n_tiles, nq, nkv, d, sink)
 
 
 def tc_row_blocks(ctas_one: int, ctas_two: int, sms: int, behind_cache: bool) -> int:

@@ -1,0 +1,368 @@
+// State-space recurrence with a short causal convolution in front (the "state-space duality"
+// layer): everything between the input projection and the output projection.
+//
+//   conv     a[t, c] = silu(b[c] + sum_k w[c, k] r[t - (taps - 1) + k, c]) over the raw channels r of
+//            the projection; inputs before the step's first token come from the request's state
+//            slot (its last taps - 1 raw inputs), inputs before the sequence's start are zero.  The
+//            tile that holds a sequence's first token of the step is the only block that touches
+//            the slot: it reads the old inputs, then writes the new ones.
+//   scan     per head h (group g = h / (heads / groups)), with u = a[:, h], B = a[:, g], C = a[:, g]:
+//              d_t = softplus(r_dt[t, h] + dt_bias[h]);   S_t = exp(-exp(A_log[h]) d_t) S_{t-1} + d_t B_t u_t^T
+//              y_t = S_t^T C_t + D[h] u_t
+//            S [N, P] lives in registers, 32-bit; a thread owns one column p and NPER rows.  A long
+//            portion is cut into chunks that run side by side in three passes: (1) every chunk from a
+//            zero state, giving its own contribution and the product of its decays; (2) the chunks'
+//            incoming states, one after the other (a handful of fused multiply-adds per element);
+//            (3) every chunk again from its incoming state, writing y.  Short portions and single
+//            tokens run pass (3) alone, from and to the state slot.
+//   gate     out[t, :] = rms_group(y[t, :] * silu(z[t, :])) * w, each of `groups` equal parts of a row
+//            divided by its own root mean square.
+//
+// All of it is 32-bit arithmetic; bfloat16 appears only as the storage type of the projection that
+// comes in and of the gated, normed row that goes out.  A sequence whose slot is negative (a dummy
+// row that pads a recorded launch) starts from zero and stores nothing.
+#include <math.h>
+#include "common.cuh"
+
+using namespace ilb;
+
+constexpr int kConvTile = 16;       // tokens of a sequence per conv block; at least the most taps - 1
+constexpr int kMaxTaps = 16;
+constexpr int kScanTokens = 16;     // tokens staged in shared memory at a time
+constexpr int kScanCols = 64;       // columns (p) of a head's state per block
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// which sequence, and which of its tiles of `tile` tokens, block `b` works on; false: none
+__device__ __forceinline__ bool find_tile(const int* __restrict__ cu_q, int n_seqs, int tile, int b, int& seq, int& index) {
+  for (seq = 0; seq < n_seqs; ++seq) {
+    const int n = (cu_q[seq + 1] - cu_q[seq] + tile - 1) / tile;
+    if (b < n) { index = b; return true; }
+    b -= n;
+  }
+  return false;
+}
+
+// ---------------------------------------------------------------- convolution
+template <typename TI, int MT>
+__global__ void __launch_bounds__(128)
+ssm_conv_kernel(const TI* __restrict__ proj, int ld, int col0, int channels, int taps, const float* __restrict__ w,
+                const float* __restrict__ bias, float* __restrict__ state, const int* __restrict__ cu_q,
+                const int* __restrict__ slots, int n_seqs, float* __restrict__ out) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  int seq, tile;
+  if (!find_tile(cu_q, n_seqs, kConvTile, blockIdx.x, seq, tile)) return;
+  const int c = blockIdx.y * 128 + threadIdx.x;
+  if (c >= channels) return;
+  const int tok0 = cu_q[seq], q_len = cu_q[seq + 1] - tok0;
+  const int slot = slots[seq];
+  const int begin = tile * kConvTile, end = min(q_len, begin + kConvTile);
+  const int before = taps - 1;
+  // the window of earlier raw inputs and the taps, both right-aligned: hist[MT - 2] is the newest
+  float hist[MT - 1], wr[MT];
+#pragma unroll
+  for (int k = 0; k < MT; ++k) {
+    const int j = k - (MT - taps);
+    wr[k] = j >= 0 ? w[(size_t)c * taps + j] : 0.f;
+  }
+#pragma unroll
+  for (int k = 0; k < MT - 1; ++k) {
+    const int j = k - (MT - 1 - before);          // 0 .. before - 1: the j-th of the `before` inputs ahead of `begin`
+    float v = 0.f;
+    if (j >= 0) {
+      const int lt = begin - before + j;
+      if (lt >= 0) v = to_float(proj[(size_t)(tok0 + lt) * ld + col0 + c]);
+      else if (slot >= 0) v = state[((size_t)slot * before + (before + lt)) * channels + c];
+    }
+    hist[k] = v;
+  }
+  const float b = bias[c];
+  for (int lt = begin; lt < end; ++lt) {
+    const float x = to_float(proj[(size_t)(tok0 + lt) * ld + col0 + c]);
+    float acc = b;
+#pragma unroll
+    for (int k = 0; k < MT - 1; ++k) acc = fmaf(wr[k], hist[k], acc);
+    acc = fmaf(wr[MT - 1], x, acc);
+    out[(size_t)(tok0 + lt) * channels + c] = silu_f(acc);
+#pragma unroll
+    for (int k = 0; k + 1 < MT - 1; ++k) hist[k] = hist[k + 1];
+    if (MT > 1) hist[MT - 2] = x;
+  }
+  if (tile == 0 && slot >= 0 && before > 0) {
+    if (q_len <= kConvTile) {
+      // the window now ends at the sequence's last token
+#pragma unroll
+      for (int k = 0; k < MT - 1; ++k) {
+        const int j = k - (MT - 1 - before);
+        if (j >= 0) state[((size_t)slot * before + j) * channels + c] = hist[k];
+      }
+    } else {
+      for (int j = 0; j < before; ++j)
+        state[((size_t)slot * before + j) * channels + c] = to_float(proj[(size_t)(tok0 + q_len - before + j) * ld + col0 + c]);
+    }
+  }
+}
+
+// proj: [T, ld] of `dtype`, the raw channels at columns col0 .. col0 + channels - 1; w: [channels, taps];
+// state: [slots, taps - 1, channels]; out: [T, channels] 32-bit; n_tiles = sum over the sequences of
+// ceil(tokens / 16).
+ILB_EXPORT int ilb_ssm_conv(const void* proj, int dtype, int ld, int col0, int channels, int taps, const float* w,
+                            const float* bias, float* state, const int* cu_q, const int* slots, int n_seqs, int n_tiles,
+                            float* out, cudaStream_t stream) {
+  ILB_REQUIRE(channels > 0 && taps >= 1 && taps <= kMaxTaps, "ssm_conv: %d channels, %d taps (at most %d)", channels, taps, kMaxTaps);
+  ILB_REQUIRE(n_seqs >= 0 && n_tiles >= 0 && ld >= col0 + channels, "ssm_conv: bad sizes");
+  if (n_tiles == 0) return 0;
+  const dim3 grid(n_tiles, (channels + 127) / 128);
+#define ILB_CONV(TI, MT) ilb::launch(ssm_conv_kernel<TI, MT>, grid, dim3(128), 0, stream, (const TI*)proj, ld, col0, channels, taps, \
+                                      w, bias, state, cu_q, slots, n_seqs, out)
+  if (dtype == kF32) { if (taps <= 4) ILB_CONV(float, 4); else ILB_CONV(float, kMaxTaps); }
+  else if (dtype == kBF16) { if (taps <= 4) ILB_CONV(__nv_bfloat16, 4); else ILB_CONV(__nv_bfloat16, kMaxTaps); }
+  else return fail("ssm_conv: unknown dtype %d", dtype);
+#undef ILB_CONV
+  return check_launch("ssm_conv");
+}
+
+// ---------------------------------------------------------------- recurrence
+struct ScanParams {
+  const float* act;        // [T, channels]: u | B | C after the convolution
+  const void* proj;        // [T, ld]: the step sizes' raw values at columns dt_col0 + h
+  const float* dt_bias; const float* a_log; const float* skip;
+  float* state;            // [slots, heads, N, P]
+  float* chunk_state;      // [chunks, heads, N, P]
+  float* chunk_decay;      // [chunks, heads]
+  float* y;                // [T, heads * P]
+  const int* cu_q; const int* slots;
+  int n_seqs, ld, dt_col0, channels, heads, P, N, groups, chunk, pass;
+};
+
+enum : int { kPassWhole = 0, kPassLocal = 1, kPassFinal = 3 };
+
+template <typename TI, int NPER>
+__global__ void __launch_bounds__(256)
+ssm_scan_kernel(const ScanParams p) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  extern __shared__ __align__(16) float smem[];
+  const int NS = blockDim.y, NP = NS * NPER;            // NP >= N, rows beyond N are zero
+  float* Bs = smem;                                      // [kScanTokens][NP]
+  float* Cs = Bs + kScanTokens * NP;                     // [kScanTokens][NP]
+  float* us = Cs + kScanTokens * NP;                     // [kScanTokens][kScanCols]
+  float* ds = us + kScanTokens * kScanCols;              // [kScanTokens] step sizes
+  float* as = ds + kScanTokens;                          // [kScanTokens] decays
+  float* ys = as + kScanTokens;                          // [kScanTokens][NS][kScanCols], when NS > 1
+  int seq, ci;
+  if (!find_tile(p.cu_q, p.n_seqs, p.chunk, blockIdx.x, seq, ci)) return;
+  const int h = blockIdx.y, g = h / (p.heads / p.groups);
+  const int tx = threadIdx.x, ty = threadIdx.y, tid = ty * kScanCols + tx, n_threads = NS * kScanCols;
+  const int col = blockIdx.z * kScanCols + tx;
+  const bool live = col < p.P;
+  const int tok0 = p.cu_q[seq], q_len = p.cu_q[seq + 1] - tok0;
+  const int begin = tok0 + ci * p.chunk, end = tok0 + min(q_len, (ci + 1) * p.chunk);
+  const int slot = p.slots[seq];
+  const int inner = p.heads * p.P;
+  const float rate = -expf(p.a_log[h]), bias = p.dt_bias[h], skip = p.skip[h];
+  const size_t per_head = (size_t)p.N * p.P;
+
+  float S[NPER];
+  {
+    const float* src = nullptr;
+    if (p.pass == kPassWhole) { if (slot >= 0) src = p.state + ((size_t)slot * p.heads + h) * per_head; }
+    else if (p.pass == kPassFinal) src = p.chunk_state + ((size_t)blockIdx.x * p.heads + h) * per_head;
+#pragma unroll
+    for (int k = 0; k < NPER; ++k) {
+      const int n = ty * NPER + k;
+      S[k] = (src != nullptr && live && n < p.N) ? src[(size_t)n * p.P + col] : 0.f;
+    }
+  }
+  float decay_all = 1.f;
+  for (int t0 = begin; t0 < end; t0 += kScanTokens) {
+    const int ts = min(kScanTokens, end - t0);
+    __syncthreads();
+    for (int i = tid; i < ts * NP; i += n_threads) {
+      const int tt = i / NP, n = i % NP;
+      const float* row = p.act + (size_t)(t0 + tt) * p.channels + inner + (size_t)g * p.N;
+      Bs[i] = n < p.N ? row[n] : 0.f;
+      Cs[i] = n < p.N ? row[(size_t)p.groups * p.N + n] : 0.f;
+    }
+    for (int i = tid; i < ts * kScanCols; i += n_threads) {
+      const int tt = i / kScanCols, c = blockIdx.z * kScanCols + i % kScanCols;
+      us[i] = c < p.P ? p.act[(size_t)(t0 + tt) * p.channels + (size_t)h * p.P + c] : 0.f;
+    }
+    if (tid < ts) {
+      const float raw = to_float(reinterpret_cast<const TI*>(p.proj)[(size_t)(t0 + tid) * p.ld + p.dt_col0 + h]);
+      const float d = softplus_f(raw + bias);
+      ds[tid] = d;
+      as[tid] = expf(rate * d);
+    }
+    __syncthreads();
+    for (int tt = 0; tt < ts; ++tt) {
+      const float u = us[tt * kScanCols + tx], a = as[tt], du = ds[tt] * u;
+      const float4* b4 = reinterpret_cast<const float4*>(Bs + tt * NP + ty * NPER);
+      const float4* c4 = reinterpret_cast<const float4*>(Cs + tt * NP + ty * NPER);
+      float acc = 0.f;
+#pragma unroll
+      for (int k = 0; k < NPER / 4; ++k) {
+        const float4 b = b4[k], c = c4[k];
+        S[4 * k + 0] = fmaf(a, S[4 * k + 0], b.x * du); acc = fmaf(S[4 * k + 0], c.x, acc);
+        S[4 * k + 1] = fmaf(a, S[4 * k + 1], b.y * du); acc = fmaf(S[4 * k + 1], c.y, acc);
+        S[4 * k + 2] = fmaf(a, S[4 * k + 2], b.z * du); acc = fmaf(S[4 * k + 2], c.z, acc);
+        S[4 * k + 3] = fmaf(a, S[4 * k + 3], b.w * du); acc = fmaf(S[4 * k + 3], c.w, acc);
+      }
+      decay_all *= a;
+      if (p.pass != kPassLocal) {
+        if (NS == 1) { if (live) p.y[(size_t)(t0 + tt) * inner + (size_t)h * p.P + col] = fmaf(skip, u, acc); }
+        else ys[(tt * NS + ty) * kScanCols + tx] = acc;
+      }
+    }
+    if (NS > 1 && p.pass != kPassLocal) {
+      __syncthreads();
+      for (int i = tid; i < ts * kScanCols; i += n_threads) {
+        const int tt = i / kScanCols, x = i % kScanCols, c = blockIdx.z * kScanCols + x;
+        if (c >= p.P) continue;
+        float acc = 0.f;
+        for (int s = 0; s < NS; ++s) acc += ys[(tt * NS + s) * kScanCols + x];
+        p.y[(size_t)(t0 + tt) * inner + (size_t)h * p.P + c] = fmaf(skip, us[tt * kScanCols + x], acc);
+      }
+    }
+  }
+  float* dst = nullptr;
+  if (p.pass == kPassWhole) { if (slot >= 0) dst = p.state + ((size_t)slot * p.heads + h) * per_head; }
+  else if (p.pass == kPassLocal) dst = p.chunk_state + ((size_t)blockIdx.x * p.heads + h) * per_head;
+  if (dst != nullptr && live) {
+#pragma unroll
+    for (int k = 0; k < NPER; ++k) {
+      const int n = ty * NPER + k;
+      if (n < p.N) dst[(size_t)n * p.P + col] = S[k];
+    }
+  }
+  if (p.pass == kPassLocal && blockIdx.z == 0 && tid == 0) p.chunk_decay[(size_t)blockIdx.x * p.heads + h] = decay_all;
+}
+
+// Pass (2): chunk_state[c] holds chunk c's own contribution; afterwards it holds the state that
+// comes INTO chunk c, and the slot holds the state after the sequence's last chunk.
+__global__ void __launch_bounds__(256)
+ssm_carry_kernel(float* __restrict__ state, float* __restrict__ chunk_state, const float* __restrict__ chunk_decay,
+                 const int* __restrict__ cu_q, const int* __restrict__ slots, int n_seqs, int chunk, int heads, int per_head) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  const int seq = blockIdx.z, h = blockIdx.y;
+  const int e = blockIdx.x * 256 + threadIdx.x;
+  if (e >= per_head) return;
+  int first = 0;
+  for (int s = 0; s < seq; ++s) first += (cu_q[s + 1] - cu_q[s] + chunk - 1) / chunk;
+  const int n = (cu_q[seq + 1] - cu_q[seq] + chunk - 1) / chunk;
+  const int slot = slots[seq];
+  float* own = slot >= 0 ? state + ((size_t)slot * heads + h) * per_head + e : nullptr;
+  float run = own != nullptr ? *own : 0.f;
+  for (int c = first; c < first + n; ++c) {
+    float* at = chunk_state + ((size_t)c * heads + h) * per_head + e;
+    const float local = *at;
+    *at = run;
+    run = fmaf(chunk_decay[(size_t)c * heads + h], run, local);
+  }
+  if (own != nullptr && n > 0) *own = run;
+}
+
+template <typename TI>
+static int scan_launch(const ScanParams& p, int n_blocks, cudaStream_t stream) {
+  const int NPER = p.N <= 16 ? 16 : (p.N <= 32 ? 32 : 64);
+  const int NS = (p.N + NPER - 1) / NPER;
+  ILB_REQUIRE(NS * kScanCols <= 256, "ssm_scan: a state of %d rows exceeds 256", p.N);
+  const int NP = NS * NPER;
+  const size_t smem = sizeof(float) * ((size_t)2 * kScanTokens * NP + kScanTokens * kScanCols + 2 * kScanTokens +
+                                       (NS > 1 ? (size_t)kScanTokens * NS * kScanCols : 0));
+  const dim3 grid(n_blocks, p.heads, (p.P + kScanCols - 1) / kScanCols), block(kScanCols, NS);
+  if (NPER == 16) ilb::launch(ssm_scan_kernel<TI, 16>, grid, block, smem, stream, p);
+  else if (NPER == 32) ilb::launch(ssm_scan_kernel<TI, 32>, grid, block, smem, stream, p);
+  else {
+    static OncePerDevice once;
+    if (once.first() && smem > 48 * 1024 &&
+        cudaFuncSetAttribute(ssm_scan_kernel<TI, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+      once.forget();
+      return fail("ssm_scan: cannot reserve %zu bytes of shared memory", smem);
+    }
+    ilb::launch(ssm_scan_kernel<TI, 64>, grid, block, smem, stream, p);
+  }
+  return check_launch("ssm_scan");
+}
+
+// act: [T, channels] 32-bit (u | B | C); proj: [T, ld] of `dtype` with the raw step sizes at dt_col0 ..;
+// state: [slots, heads, N, P]; y: [T, heads * P].  chunk = 0: every sequence in one run from and to its
+// slot (n_blocks = n_seqs).  chunk > 0: three passes over chunks of that many tokens, n_blocks = the
+// sum over the sequences of ceil(tokens / chunk), chunk_state [n_blocks, heads, N, P], chunk_decay
+// [n_blocks, heads].
+ILB_EXPORT int ilb_ssm_scan(const float* act, const void* proj, int dtype, int ld, int dt_col0, int channels,
+                            const float* dt_bias, const float* a_log, const float* skip, float* state, float* chunk_state,
+                            float* chunk_decay, float* y, const int* cu_q, const int* slots, int n_seqs, int heads, int P, int N,
+                            int groups, int chunk, int n_blocks, cudaStream_t stream) {
+  ILB_REQUIRE(heads > 0 && P > 0 && N > 0 && groups > 0 && heads % groups == 0, "ssm_scan: bad sizes");
+  ILB_REQUIRE(channels == heads * P + 2 * groups * N, "ssm_scan: %d channels for %d heads of %d, %d groups of %d", channels, heads, P, groups, N);
+  ILB_REQUIRE(heads <= 65535 && n_seqs <= 65535, "ssm_scan: too many heads or sequences");
+  ILB_REQUIRE(dtype == kF32 || dtype == kBF16, "ssm_scan: unknown dtype %d", dtype);
+  ILB_REQUIRE(chunk >= 0 && (chunk == 0 || (chunk_state != nullptr && chunk_decay != nullptr)), "ssm_scan: chunks need their scratch");
+  if (n_blocks <= 0 || n_seqs <= 0) return 0;
+  ScanParams p;
+  p.act = act; p.proj = proj; p.dt_bias = dt_bias; p.a_log = a_log; p.skip = skip; p.state = state;
+  p.chunk_state = chunk_state; p.chunk_decay = chunk_decay; p.y = y; p.cu_q = cu_q; p.slots = slots;
+  p.n_seqs = n_seqs; p.ld = ld; p.dt_col0 = dt_col0; p.channels = channels; p.heads = heads; p.P = P; p.N = N;
+  p.groups = groups;
+  auto run = [&](int pass) {
+    p.pass = pass;
+    return dtype == kF32 ? scan_launch<float>(p, n_blocks, stream) : scan_launch<__nv_bfloat16>(p, n_blocks, stream);
+  };
+  if (chunk == 0) { p.chunk = 1 << 30; return run(kPassWhole); }
+  p.chunk = chunk;
+  if (int rc = run(kPassLocal)) return rc;
+  const int per_head = N * P;
+  ilb::launch(ssm_carry_kernel, dim3((per_head + 255) / 256, heads, n_seqs), dim3(256), 0, stream, state, chunk_state,
+              (const float*)chunk_decay, cu_q, slots, n_seqs, chunk, heads, per_head);
+  if (int rc = check_launch("ssm_carry")) return rc;
+  return run(kPassFinal);
+}
+
+// ---------------------------------------------------------------- gate and grouped norm
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+gated_group_norm_kernel(const float* __restrict__ y, const TI* __restrict__ gate, int ld_gate, const float* __restrict__ w,
+                        TO* __restrict__ out, int width, int groups, float eps) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  __shared__ float scratch[33];
+  const int t = blockIdx.x, part = blockIdx.y, n = width / groups;
+  const float* yr = y + (size_t)t * width + (size_t)part * n;
+  const TI* zr = gate + (size_t)t * ld_gate + (size_t)part * n;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = yr[i] * silu_f(to_float(zr[i]));
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+  TO* o = out + (size_t)t * width + (size_t)part * n;
+  for (int i = threadIdx.x; i < n; i += blockDim.x)
+    o[i] = from_float<TO>(yr[i] * silu_f(to_float(zr[i])) * inv * w[(size_t)part * n + i]);
+}
+
+// out[t, :] = rms over each of `groups` equal parts of (y[t, :] * silu(gate[t, :])) * w; gate is [T, ld_gate] of
+// `dtype` (its first `width` columns), out [T, width] of `dtype`.
+ILB_EXPORT int ilb_gated_group_norm(const float* y, const void* gate, int dtype, int ld_gate, const float* w, void* out,
+                                    int rows, int width, int groups, float eps, cudaStream_t stream) {
+  ILB_REQUIRE(rows >= 0 && width > 0 && groups > 0 && width % groups == 0 && groups <= 65535, "gated_group_norm: bad sizes");
+  ILB_REQUIRE(eps > 0.f, "gated_group_norm: eps must be positive");
+  if (rows == 0) return 0;
+  const int n = width / groups;
+  const int threads = n >= 1024 ? 256 : (n >= 256 ? 128 : 64);
+  if (dtype == kF32)
+    ilb::launch(gated_group_norm_kernel<float, float>, dim3(rows, groups), dim3(threads), 0, stream, y, (const float*)gate, ld_gate, w,
+                (float*)out, width, groups, eps);
+  else if (dtype == kBF16)
+    ilb::launch(gated_group_norm_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(rows, groups), dim3(threads), 0, stream, y,
+                (const __nv_bfloat16*)gate, ld_gate, w, (__nv_bfloat16*)out, width, groups, eps);
+  else
+    return fail("gated_group_norm: unknown dtype %d", dtype);
+  return check_launch("gated_group_norm");
+}
+
+ILB_DEFINE_LAST_ERROR()

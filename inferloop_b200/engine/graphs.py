@@ -143,7 +143,7 @@ class DecodeGraphs:
         hidden_of: Dict[str, torch.Tensor] = {}
 
         def embed():
-            hidden_of["h"] = model.forward_embed(ctx)
+            hidden_of["h"] = model.forward_embed(ctx, cache)
 
         def entries(first, last):
             return lambda: model.forward_entries(hidden_of["h"], ctx, cache, first, last)

@@ -214,7 +214,8 @@ class ModelRunner:
         self.model = DecoderModel(spec, self.ctx)
         self.model.bind(tensors)
         self.cache = CacheManager(self.model.cache_needs(), page_size, num_pages, max_requests,
-                                  dtype=dtype, device=device, run_order=spec.run_order)
+                                  dtype=dtype, device=device, run_order=spec.run_order,
+                                  model_slots=self.model.model_slot_needs())
         self.stager = StepStager(device)
         self.steps_run = 0
         self.tokens_run = 0
@@ -271,7 +272,8 @@ class ModelRunner:
         self.cache = None
         torch.cuda.empty_cache()
         self.cache = CacheManager(self.model.cache_needs(), page_size, num_pages, max_requests,
-                                  dtype=self.dtype, device=self.device, run_order=self.spec.run_order)
+                                  dtype=self.dtype, device=self.device, run_order=self.spec.run_order,
+                                  model_slots=self.model.model_slot_needs())
         if self.graphs is not None:          # recorded graphs point into the old cache
             from .graphs import DecodeGraphs
             self.graphs = DecodeGraphs(self, -(-self.spec.max_positions // page_size))

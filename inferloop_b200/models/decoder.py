@@ -28,6 +28,7 @@ class DecoderModel:
         self.final_norm = registry.build_norm(
             spec.final_norm, ctx, _strip_weight(spec.final_norm_name), width=spec.hidden_size)
         self.logits_post = (registry.build("logits", spec.logits_post, ctx) if spec.logits_post is not None else None)
+        self.embed_part = registry.build("embedding", spec.embedding, ctx) if spec.embedding is not None else None
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self._weight_bytes = 0
@@ -36,6 +37,8 @@ class DecoderModel:
     def declare_weights(self) -> List[WeightDecl]:
         s = self.spec
         out = [WeightDecl(s.embedding_name, (s.vocab_size, s.hidden_size), role="table")]
+        if self.embed_part is not None:
+            out += self.embed_part.declare_weights()
         for b in self.blocks:
             out += b.declare_weights()
         out += self.final_norm.declare_weights()
@@ -50,6 +53,8 @@ class DecoderModel:
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         s = self.spec
         self.embedding = tensors[s.embedding_name].contiguous()
+        if self.embed_part is not None:
+            self.embed_part.bind(tensors)
         for b in self.blocks:
             b.bind(tensors)
         self.final_norm.bind(tensors)
@@ -62,6 +67,10 @@ class DecoderModel:
     def cache_needs(self) -> List[CacheNeeds]:
         return [b.cache_needs() for b in self.blocks]
 
+    def model_slot_needs(self):
+        """State per request that belongs to the model as a whole (the embedding part's)."""
+        return tuple(self.embed_part.cache_needs().slots) if self.embed_part is not None else ()
+
     def weight_bytes(self) -> int:
         """Bytes of every weight one step reads once: the tensors the parts declared, as they
         were bound (the token table is read by row only, unless it is the output matrix too)."""
@@ -71,7 +80,8 @@ class DecoderModel:
     def graph_safe(self) -> bool:
         """Whether embedding, final norm, output matrix and the logits map read the batch from
         device memory alone (the blocks answer for themselves)."""
-        return self.final_norm.graph_safe and (self.logits_post is None or self.logits_post.graph_safe)
+        return (self.final_norm.graph_safe and (self.logits_post is None or self.logits_post.graph_safe)
+                and (self.embed_part is None or self.embed_part.graph_safe))
 
     def scratch_bytes(self, tokens: int, logit_rows: int) -> int:
         """Workspace a step of `tokens` tokens with `logit_rows` wanted rows asks for: the
@@ -80,6 +90,7 @@ class DecoderModel:
         s = self.spec
         size = torch.empty((), dtype=self.ctx.dtype).element_size()
         blocks = max((b.scratch_bytes(tokens) for b in self.blocks), default=0)
+        blocks += self.embed_part.scratch_bytes(tokens) if self.embed_part is not None else 0
         return (tokens * s.hidden_size * s.residual_streams * 4 + blocks + logit_rows * s.hidden_size * (4 + size)
                 + logit_rows * s.vocab_size * 4)
 
@@ -87,7 +98,7 @@ class DecoderModel:
     def forward(self, step, caches) -> torch.Tensor:
         """Run the step's tokens through every run-order entry; returns 32-bit logits
         [len(step.logit_rows), vocab] (a workspace buffer, valid until the next step)."""
-        hidden = self.forward_embed(step)
+        hidden = self.forward_embed(step, caches)
         self.forward_entries(hidden, step, caches, 0, len(self.spec.run_order))
         return self.forward_head(hidden, step)
 
@@ -97,10 +108,13 @@ class DecoderModel:
         s = self.spec
         return self.ctx.workspace.buffer("model.hidden", (tokens, s.residual_streams * s.hidden_size), torch.float32)
 
-    def forward_embed(self, step) -> torch.Tensor:
+    def forward_embed(self, step, caches=None) -> torch.Tensor:
         s = self.spec
         hidden = self.hidden_buffer(step.n_tokens)
         ops.scope("embedding")
+        if self.embed_part is not None:
+            self.embed_part.forward(step, self.embedding, hidden, caches.model_state() if caches is not None else {})
+            return hidden
         ops.embed(step.tokens, self.embedding, hidden, 1.0 if s.embedding_scale is None else float(s.embedding_scale),
                   s.residual_streams)
         return hidden

@@ -12,6 +12,7 @@ model-specific reaches it through its spec.
   FeedForward       forward(x, residual, step)                           residual += ffn(x)
   Block             cache_needs(); forward(hidden, step, cache)          hidden updated in place
   LogitsPost        forward(logits)                                      logits mapped in place
+  Embedding         cache_needs(); forward(step, table, hidden, state)   token ids -> residual stream
 
 `hidden` / `residual` is the 32-bit residual stream [tokens, hidden]; `x` is a normed
 copy in the compute dtype.  `step` is the :class:`~inferloop_b200.engine.batch.StepContext`
@@ -88,7 +89,7 @@ class PagedKVNeed:
     kv_heads: int
     head_dim: int
     window: Optional[int] = None     # None: all keys are kept; n: only the last n are read
-    v_head_dim: Optional[int] = None  # head size of the values when it is not the keys'
+    v_head_dim: Optional[int] = None  # head size of the values when it is not the keys'; 0: the cached vector is all there is
 
     @property
     def value_dim(self) -> int:
@@ -157,6 +158,15 @@ class FeedForward(Part):
 
 class Block(Part):
     def forward(self, hidden: torch.Tensor, step, cache) -> None:
+        raise NotImplementedError
+
+
+class Embedding(Part):
+    """Turns the step's token ids into the 32-bit residual stream.  `table` is the model's
+    token table (the model owns it: it may be the output matrix too); `state` holds the
+    tensors of this part's slot needs, [slots, *shape] each."""
+
+    def forward(self, step, table: torch.Tensor, hidden: torch.Tensor, state: Mapping[str, torch.Tensor]) -> None:
         raise NotImplementedError
 
 

@@ -2,8 +2,9 @@
 
   z = W_router x                (32-bit; x may be the compute dtype's rounding)
   s = sigmoid(z)  or  softmax(z) over the experts          (`score`)
+  (`router_bias`: z = W_router x + b)
   the top_k experts with the largest s (ties to the lower index), weights w = their s,
-  divided by their sum when `renormalize`
+  divided by their sum when `renormalize` (softmax + renormalize = the softmax over the chosen logits alone)
   y = sum_j expert_j(w_j x)     (`weight_on` = "input")   or   sum_j w_j expert_j(x)   ("output")
   y += sigmoid(W_gate x) * shared(x)    when the description has a shared expert (`shared_inter`;
   `shared_gate` False leaves the multiplier out)
@@ -46,6 +47,18 @@ class RoutedExperts(FeedForward):
         self.score = str(spec.get("score", "softmax"))
         self.renormalize = bool(spec.get("renormalize", False))
         self.weight_on = str(spec.get("weight_on", "output"))
+        self.router_bias = bool(spec.get("router_bias", False))       # a vector added to the router's logits
+        # the experts' gated unit: a(gate) * (up + up_offset), a(g) = g * sigmoid(sharpness * g); kind "clamped_glu" also
+        # takes min(gate, limit) and clamp(up, -limit, limit) first.  (limit, sharpness, up_offset); the default is SwiGLU.
+        act = spec.get("activation")
+        if act is None or act.kind == "swiglu":
+            self.act = (0.0, 1.0, 0.0)
+        elif act.kind == "clamped_glu":
+            self.act = (float(act["limit"]), float(act.get("sharpness", 1.0)), float(act.get("up_offset", 0.0)))
+            if self.act[0] <= 0:
+                raise ValueError("clamped_glu: limit must be positive")
+        else:
+            raise ValueError(f"the experts' activation must be 'swiglu' or 'clamped_glu', found {act.kind!r}")
         self.shared_inter = int(spec.get("shared_inter") or 0)
         self.shared_gate = bool(spec.get("shared_gate", False)) and self.shared_inter > 0
         if self.score not in ("sigmoid", "softmax"):
@@ -55,7 +68,7 @@ class RoutedExperts(FeedForward):
         if not 0 < self.top <= self.experts:
             raise ValueError(f"top_k {self.top} of {self.experts} experts")
         # tensor names under the prefix: {e} is the expert's number
-        names = {"router": "router.weight", "gate": "experts.{e}.gate_proj.weight", "up": "experts.{e}.up_proj.weight",
+        names = {"router": "router.weight", "router_bias": "router.bias", "gate": "experts.{e}.gate_proj.weight", "up": "experts.{e}.up_proj.weight",
                  "down": "experts.{e}.down_proj.weight", "shared_gate": "shared_expert_gate.weight",
                  "shared_prefix": "shared_expert."}
         for role, name in spec.get("names", ()):
@@ -67,13 +80,15 @@ class RoutedExperts(FeedForward):
         if self.shared_inter:
             self.shared = SwiGLU(PartSpec.make("swiglu", hidden_size=self.hidden, intermediate_size=self.shared_inter,
                                                names=tuple(spec.get("shared_names", ()))), ctx, self.names["shared_prefix"])
-        self.w_router = self.w_gate_up = self.w_down = None
+        self.w_router = self.w_gate_up = self.w_down = self.b_router = None
         self.fused = False          # gate/up rows interleaved for the tensor-core product's SwiGLU epilogue
 
     # ------------------------------------------------------------------ weights
     def declare_weights(self) -> List[WeightDecl]:
         n, H, I = self.names, self.hidden, self.inter
         out = [WeightDecl(n["router"], (self.experts, H))]
+        if self.router_bias:
+            out.append(WeightDecl(n["router_bias"], (self.experts,), "vector", "bias"))
         for e in range(self.experts):
             out += [WeightDecl(n["gate"].format(e=e), (I, H)), WeightDecl(n["up"].format(e=e), (I, H)),
                     WeightDecl(n["down"].format(e=e), (H, I))]
@@ -87,6 +102,8 @@ class RoutedExperts(FeedForward):
         n = self.names
         rows = [tensors[n["router"]]] + ([tensors[n["shared_gate"]]] if self.shared_gate else [])
         self.w_router = torch.cat(rows, dim=0).contiguous()
+        if self.router_bias:
+            self.b_router = tensors[n["router_bias"]].contiguous()
         gates = [tensors[n["gate"].format(e=e)] for e in range(self.experts)]
         ups = [tensors[n["up"].format(e=e)] for e in range(self.experts)]
         self.fused = gates[0].dtype == torch.bfloat16 and self.inter % 64 == 0 and self.hidden % 8 == 0
@@ -132,7 +149,7 @@ class RoutedExperts(FeedForward):
         ops.moe_logits(x, self.w_router, logits)
         choice = ws.buffer("moe.choice", (T * K,), torch.int32)
         weight = ws.buffer("moe.weight", (T * K,), torch.float32)
-        ops.moe_route(logits, E, K, self.score == "softmax", self.renormalize, choice, weight)
+        ops.moe_route(logits, E, K, self.score == "softmax", self.renormalize, choice, weight, bias=self.b_router)
         pos = ws.buffer("moe.pos", (T * K,), torch.int32)
         block_expert = ws.buffer("moe.block_expert", (rows // block,), torch.int32)
         ops.moe_plan(choice, E, block, pos, block_expert)
@@ -144,12 +161,15 @@ class RoutedExperts(FeedForward):
         if self.fused:
             if not (ops.moe_gemm_tc_eligible(a, self.w_gate_up, swiglu=True) and ops.moe_gemm_tc_eligible(act, self.w_down)):
                 raise ops.KernelError("routed experts: the interleaved weights need the tensor-core product, which refused this input")
-            ops.moe_gemm_tc(a, self.w_gate_up, act, block_expert, swiglu=True, block_rows=block)
+            ops.moe_gemm_tc(a, self.w_gate_up, act, block_expert, swiglu=True, block_rows=block, act=self.act)
             ops.moe_gemm_tc(act, self.w_down, routed, block_expert, block_rows=block)
         else:
             gate_up = ws.buffer("moe.gate_up", (rows, 2 * I), dt)
             ops.gemm_simt_grouped(a, self.w_gate_up, gate_up, block_expert)
-            ops.silu_mul(gate_up, act)
+            if self.act == (0.0, 1.0, 0.0):
+                ops.silu_mul(gate_up, act)
+            else:
+                ops.glu_mul(gate_up, act, *self.act)
             ops.gemm_simt_grouped(act, self.w_down, routed, block_expert)
         shared_out = None
         if self.shared is not None:

@@ -16,20 +16,24 @@ from .registry import register
 class RMSNorm(Norm):
     graph_safe = True
     """spec: eps; optional `weight_suffix` (default "weight"): the weight is the tensor
-    prefix + suffix, of the width that the owner gives."""
+    prefix + suffix, of the width that the owner gives; optional `offset` (default 0): the
+    stored tensor is the weight minus this constant (a weight kept around zero: offset 1)."""
 
     def __init__(self, spec, ctx, prefix: str = "", width: int = 0, name: str = "weight") -> None:
         super().__init__(spec, ctx, prefix)
         self.eps = float(spec["eps"])
         self.width = int(width or spec.get("width", 0))
         self.weight_name = prefix + str(spec.get("weight_suffix", name))
+        self.offset = float(spec.get("offset", 0.0))
         self.weight = None
 
     def declare_weights(self) -> List[WeightDecl]:
-        return [WeightDecl(self.weight_name, (self.width,), role="vector", init="norm")]
+        return [WeightDecl(self.weight_name, (self.width,), role="vector", init="around_zero" if self.offset else "norm")]
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.weight = tensors[self.weight_name].contiguous()
+        if self.offset:
+            self.weight = (self.weight + self.offset).contiguous()      # 32-bit: the sum a norm in 32-bit would form
 
     def forward(self, x: torch.Tensor, out: torch.Tensor) -> None:
         ops.rmsnorm(x, self.weight, self.eps, out)

@@ -6,7 +6,7 @@ from typing import Callable, Dict, Type
 from ..config.spec import PartSpec
 from .base import BuildContext, Part
 
-ROLES = ("norm", "position", "mixer", "feed_forward", "block", "logits")
+ROLES = ("norm", "position", "mixer", "feed_forward", "block", "logits", "embedding")
 _REGISTRY: Dict[str, Dict[str, Type[Part]]] = {r: {} for r in ROLES}
 
 
@@ -65,4 +65,4 @@ def _ensure_builtin() -> None:
     if _BUILTIN_DONE:
         return
     _BUILTIN_DONE = True
-    from . import attention, block, hyper, logits, mlp, moe, norm, rope  # noqa: F401  (they register themselves)
+    from . import attention, block, embedding, hyper, latent_attention, logits, loop, mlp, moe, norm, rope, ssm  # noqa: F401  (they register themselves)
