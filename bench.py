@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
                     [--config 8b|14b-mixed|32b-long] [--breakdown] [--kernels [attention|products]] [--further]
-                    [--sufolix [dense|moe]]
+                    [--sufolix [dense|moe]] [--mamevik [latent|ssd|mixed]]
 
 One JSON line on stdout.  The default (`--config 8b`) is the headline: Qwen3-8B layer sizes,
 36 layers, batch 8, 1,024-token prompts; a "step" is one decode step of the whole batch.
@@ -31,6 +31,9 @@ sizes: decode at batches 16 to 256, a prompt of 32,768 tokens in portions, the 3
 `--sufolix` measures the Sufolix decoder (several residual streams, its attention variants, routed experts) at
 two layer sizes, dense and routed, beside a Qwen3 model of equal width, heads, layers and active feed-forward size:
 decode at --batch, one 2,048-token prompt, and the per-op-class device time of both.
+`--mamevik` measures the Mamevik decoder (attention over a cached latent with a sink, state-space recurrences, a looped span
+of layers, clamped gated experts) the same way, in three arrangements of its layers, beside a Sufolix model with routed
+experts of the same width, layers and experts.
 Peaks come from MEASURED_PEAKS.json beside this file when present, else the fallback
 figures 6.65 TB/s and 1.59 PFLOP/s.  Weights (15 GB and more) exceed L2 (126 MB), so every
 step reads them from HBM: no L2 flush is needed between timed steps.
@@ -163,10 +166,43 @@ def sufolix_numbers(cfg: dict):
     return {"layer_params": params / L, "head_params": V * W, "kv_bytes_per_token": kv, "attn_flops_per_pair": attn, "layers": L}
 
 
+def mamevik_numbers(cfg: dict):
+    """The same for a Mamevik configuration: per layer run (a looped layer counts every time) the parameters one
+    token's products touch, the cached latent's bytes, and the flops of a (query, key) pair with keys and values both
+    being the latent.  `state_bytes_per_seq`: what a decode step reads and writes of a sequence's recurrent state."""
+    W, V = cfg["width"], cfg["vocab"]
+    loop = cfg.get("loop")
+    runs = [1] * len(cfg["layers"])
+    if loop:
+        for i in range(loop["start"], loop["stop"]):
+            runs[i] = loop["times"]
+    params, kv, attn, state = 0, 0, 0, 0
+    for layer, n in zip(cfg["layers"], runs):
+        m, f = layer["mixer"], layer["mlp"]
+        if layer["type"] == "mamba2":
+            inner = m["heads"] * m["vdim"]
+            params += n * (2 * inner + 2 * m["groups"] * m["state"] + m["heads"] + inner) * W
+            state += n * 2 * 4 * (m["heads"] * m["state"] * m["vdim"] + (m["conv"] - 1) * (inner + 2 * m["groups"] * m["state"]))
+        else:
+            params += n * ((m["heads"] * m["dim"] + m["kv_rank"]) * W + m["heads"] * (m["dim"] + m["vdim"]) * m["kv_rank"]
+                           + m["heads"] * m["vdim"] * W)
+            kv += n * m["kv_rank"] * 2
+            attn += n * 4 * m["heads"] * m["kv_rank"]
+        if f is not None:
+            params += n * (3 * W * f["router"]["top"] * f["expert"]["ff"] + W * f["router"]["experts"])
+    if loop:
+        params += loop["times"] * 2 * W * W
+    L = sum(runs)
+    return {"layer_params": params / L, "head_params": V * W, "kv_bytes_per_token": kv, "attn_flops_per_pair": attn, "layers": L,
+            "state_bytes_per_seq": state}
+
+
 def model_numbers(cfg: dict):
     """Parameters the matrix products of one token touch, and bytes of cache per token."""
     if cfg.get("architecture") == "Sufolix":
         return sufolix_numbers(cfg)
+    if cfg.get("architecture") == "Mamevik":
+        return mamevik_numbers(cfg)
     H, I, V, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
     nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     per_layer = (nq + 2 * nkv) * d * H + nq * d * H + 3 * H * I
@@ -709,6 +745,68 @@ def run_sufolix(args) -> dict:
     return out
 
 
+# ----------------------------------------------------------------------------- the Mamevik decoder beside Sufolix
+def mamevik_config(kind: str, layers: int, width: int, vocab: int, experts: int, top: int, expert_ff: int) -> dict:
+    """`kind`: "latent" (every layer attends over a cached latent), "ssd" (every layer is a state-space recurrence) or
+    "mixed" (they alternate, and the two middle layers run twice)."""
+    latent = {"type": "latent_attention", "mixer": {"heads": 16, "dim": 128, "vdim": 128, "kv_rank": 128, "scale": 128 ** -0.5,
+                                                    "mask": {"size": 4096}}}
+    ssd = {"type": "mamba2", "mixer": {"heads": 32, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 1}}
+    mlp = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff, "limit": 7.0}}
+    pick = {"latent": lambda i: latent, "ssd": lambda i: ssd, "mixed": lambda i: ssd if i % 2 else latent}[kind]
+    cfg = {"architecture": "Mamevik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+           "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
+           "layers": [dict(pick(i), mlp=dict(mlp)) for i in range(layers)], "logit_scale": 1.0, "logit_softcap": 30.0}
+    if kind == "mixed":
+        cfg["loop"] = {"start": layers // 2 - 1, "stop": layers // 2 + 1, "times": 2}
+    return cfg
+
+
+def run_mamevik(args) -> dict:
+    """Decode and prefill of the Mamevik decoder at layer sizes of a real model (attention over a cached latent,
+    state-space recurrences, both with a loop), each beside the closest model the engine has, the Sufolix decoder with
+    routed experts at the same width, layers and experts; with the device time of every op class."""
+    import torch
+    L, W, V = args.layers if args.layers != FULL_LAYERS else 8, 2048, 32768
+    E, TOP, EFF = 16, 2, 1408
+    which = ["latent", "ssd", "mixed"] if args.mamevik == "all" else [args.mamevik]
+    out = {"metric": "mamevik_vs_sufolix_equal_size", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic",
+           "steps": args.steps, "warmup": args.warmup, "batch": args.batch, "peaks": peaks(), "cases": {}}
+    arms = {kind: mamevik_config(kind, L, W, V, E, TOP, EFF) for kind in which}
+    arms["sufolix"] = sufolix_config("moe", L, W, 16, 4, 128, 0, E, TOP, EFF, 0, V, 1)
+    arms["sufolix"].pop("streams")
+    for layer in arms["sufolix"]["layers"]:
+        layer["mlp"].pop("shared")
+    for arm, cfg in arms.items():
+        pages = (args.batch * (PROMPT_LEN + args.steps + args.warmup + 64) + PREFILL_LEN) // PAGE + 64
+        bench = Bench(cfg, SEED, pages, max(args.batch, 8), 8192, PREFILL_LEN)
+        with ClockSampler() as clocks:
+            tps, ms, kernels, ctx = bench.decode_device(args.batch, args.steps, args.warmup, arm, PROMPT_LEN)
+        runs = bench.nums["layers"]
+        touched = bench.weight_bytes - runs * 3 * W * EFF * 2 * max(0, E - min(E, args.batch * TOP))
+        if cfg.get("loop"):                   # a looped layer's weights are read on every run
+            touched += (runs - len(cfg["layers"])) * (bench.weight_bytes - V * W * 2) / len(cfg["layers"])
+        step_bytes = touched + args.batch * (ctx * bench.nums["kv_bytes_per_token"] + bench.nums.get("state_bytes_per_seq", 0))
+        r = {"decode_tokens_per_s": round(tps, 1), "decode_ms_per_step": round(ms, 4), "kernels_per_step": kernels,
+             "layer_runs": runs, "decode_frac_of_hbm": round(step_bytes / (ms / 1e3) / 1e9 / bench.pk["hbm_gbs"], 4),
+             "weights_gb": round(bench.weight_bytes / 1e9, 3), "clocks": clocks.summary(),
+             "prefill": bench.prefill_timed(PREFILL_LEN, 3, PREFILL_SAMPLES)}
+        if args.breakdown:
+            r["breakdown"] = bench.breakdown(args.batch, PROMPT_LEN, PREFILL_LEN)
+        out["cases"][arm] = r
+        del bench
+        torch.cuda.empty_cache()
+    out["sizes"] = {"layers": L, "width": W, "vocab": V, "experts": E, "top": TOP, "expert_ff": EFF,
+                    "latent": arms[which[0]]["layers"][0]["mixer"] if which[0] != "ssd" else None,
+                    "sufolix": {"heads": 16, "kv_heads": 4, "head_dim": 128}}
+    base = out["cases"]["sufolix"]
+    for kind in which:
+        c = out["cases"][kind]
+        c["decode_ms_per_layer_run_over_sufolix"] = round((c["decode_ms_per_step"] / c["layer_runs"]) / (base["decode_ms_per_step"] / L), 4)
+        c["prefill_ms_per_layer_run_over_sufolix"] = round((c["prefill"]["ms"] / c["layer_runs"]) / (base["prefill"]["ms"] / L), 4)
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -725,6 +823,8 @@ def main() -> int:
                     help="time kernels alone at the layer sizes of --config")
     ap.add_argument("--sufolix", nargs="?", const="all", default=None, choices=["all", "dense", "moe"],
                     help="the Sufolix decoder beside a Qwen3 model of equal size (decode, prefill, op classes with --breakdown)")
+    ap.add_argument("--mamevik", nargs="?", const="all", default=None, choices=["all", "latent", "ssd", "mixed"],
+                    help="the Mamevik decoder beside a Sufolix model with routed experts of equal size (decode, prefill, op classes with --breakdown)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -745,6 +845,9 @@ def main() -> int:
         return 0
     if args.sufolix:
         print(json.dumps(run_sufolix(args)))
+        return 0
+    if args.mamevik:
+        print(json.dumps(run_mamevik(args)))
         return 0
     result = {"8b": run_8b, "14b-mixed": run_14b_mixed, "32b-long": run_32b_long}[args.config](args)
     print(json.dumps(result))

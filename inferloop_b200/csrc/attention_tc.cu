@@ -140,6 +140,7 @@ struct Params {
   int max_blocks, n_seqs, nq, nkv, window, out_stride, page_size, num_pages;
   float scale_log2;
   int skip_single;       // sequences that bring one token are somebody else's (the decode kernel's)
+  const float* sink;     // [nq] or null: a logit per query head that joins the softmax's denominator unscaled, without a value
 };
 
 // QB = row blocks of a CTA.  Measured on this part (one thread issuing, operands in place): a
@@ -515,6 +516,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     xmax[512 + half * 128 + row] = l;
     block_sync();
     l += xmax[512 + (half ^ 1) * 128 + row];
+    // the sink's term, relative to the maximum the sums were taken against (both halves of a row share it)
+    if (p.sink != nullptr && live && l > 0.f) l += exp2f(p.sink[head] * kLog2e - m_used);
     if (ok) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* dst = p.out + (size_t)(tok0 + (live ? tl : 0)) * p.out_stride + (size_t)head * D + half * kOCols;
@@ -595,7 +598,7 @@ ILB_EXPORT int ilb_attention_prefill_tc(const void* q, void* out, const void* k_
                                         const int* positions, const int* cu_q, const int* block_table,
                                         int max_blocks, int page_size, int num_pages, int window, float scale,
                                         int n_tokens, int n_seqs, int n_tiles, int row_blocks, int skip_single, int nq, int nkv, int d,
-                                        int q_stride, int out_stride, int* error_flag, cudaStream_t stream) {
+                                        int q_stride, int out_stride, int* error_flag, const float* sink, cudaStream_t stream) {
   ILB_REQUIRE(row_blocks == 1 || row_blocks == 2, "attention (tensor cores): %d row blocks per CTA (1 or 2)", row_blocks);
   ILB_REQUIRE(ilb_attention_tc_supported(nq, nkv, d, page_size),
               "attention (tensor cores): heads %d/%d, head size %d, page size %d are not built", nq, nkv, d, page_size);
@@ -632,7 +635,7 @@ ILB_EXPORT int ilb_attention_prefill_tc(const void* q, void* out, const void* k_
     if (encode(&mvr, v_cache, 5, rdims, rstrides, run, "v cache (page run)")) return -1;
   }
   Params p{(__nv_bfloat16*)out, positions, cu_q, block_table, error_flag, max_blocks, n_seqs, nq, nkv, window,
-           out_stride, page_size, num_pages, scale * kLog2e, skip_single ? 1 : 0};
+           out_stride, page_size, num_pages, scale * kLog2e, skip_single ? 1 : 0, sink};
   if (row_blocks == 2)
     return d == 64 ? launch<64, 2>(mq, mk, mv, mkr, mvr, p, n_tiles, stream) : launch<128, 2>(mq, mk, mv, mkr, mvr, p, n_tiles, stream);
   return d == 64 ? launch<64, 1>(mq, mk, mv, mkr, mvr, p, n_tiles, stream) : launch<128, 1>(mq, mk, mv, mkr, mvr, p, n_tiles, stream);

@@ -744,7 +744,7 @@ def attention_tc_supported(nq: int, nkv: int, d: int, page_size: int) -> bool:
 
 
 def attention_prefill_tc(q, out, k_cache, v_cache, positions, cu_q, block_table, window, scale, n_seqs,
-                         n_tiles, nq, nkv, d, row_blocks: int = 1, skip_single: bool = False) -> None:
+                         n_tiles, nq, nkv, d, row_blocks: int = 1, skip_single: bool = False, sink=None) -> None:
     """Prefill attention on tcgen05 tensor cores (attention_tc.cu); a CTA takes `row_blocks`
     (1 or 2) blocks of 128 // (nq / nkv) tokens of one sequence, and n_tiles counts the CTAs
     over the sequences (with `skip_single`, over those that bring more than one token: the
@@ -756,7 +756,7 @@ def attention_prefill_tc(q, out, k_cache, v_cache, positions, cu_q, block_table,
     _call("attention_tc", "ilb_attention_prefill_tc", _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache),
           _ptr(positions), _ptr(cu_q), _ptr(block_table), _i(block_table.shape[1]), _i(page_size),
           _i(num_pages), _i(window or 0), _f(scale), _i(q.shape[0]), _i(n_seqs), _i(n_tiles), _i(row_blocks), _i(1 if skip_single else 0), _i(nq), _i(nkv),
-          _i(d), _i(q.shape[1]), _i(out.shape[1]), _ptr(st.error), _stream(q))
+          _i(d), _i(q.shape[1]), _i(out.shape[1]), _ptr(st.error), _ptr(sink), _stream(q))
 
 
 def attention_prefill(q, out, k_cache, v_cache, positions, cu_q, block_table, window, scale, n_seqs,
@@ -878,7 +878,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
                                block_table, window, scale, nq, nkv, d, dv, sink)
         return
     G = nq // nkv
-    # (the cluster-merged decode kernel and the tcgen05 prefill kernel take no sink: such layers use the mma.sync kernels)
+    # (the cluster-merged decode kernel takes no sink: single tokens of such layers go to the ticketed split-KV kernel)
     if step.decode_only and DECODE_CLUSTER_ENABLED and sink is None and attention_decode_tma_supported(nq, nkv, d, k_cache.shape[2]):
         attention_decode_tma(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,
                              step.n_seqs, nq, nkv, d, getattr(step, "max_kv_len", 0) >= DECODE_LONG_CONTEXT)
@@ -890,12 +890,12 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
         tickets = workspace.zeroed("attn.decode_tickets", (max(step.n_seqs * nkv, 4096),), torch.int32)
         attention_decode(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,
                          step.n_seqs, nq, nkv, d, decode_chunk, max_chunks, scratch, tickets, sink)
-    elif TC_ATTENTION_ENABLED and sink is None and attention_tc_supported(nq, nkv, d, k_cache.shape[2]):
+    elif TC_ATTENTION_ENABLED and attention_tc_supported(nq, nkv, d, k_cache.shape[2]):
         # A mixed step: the sequences that bring one token go to the split-KV decode kernel
         # (it leaves the others alone), the portions to the prefill kernel (which leaves those).
         lens = step.h_q_len
         kv_lens = getattr(step, "h_kv_len", None) or lens
-        split = (MIXED_SPLIT_ENABLED and DECODE_CLUSTER_ENABLED and 1 in lens and max(lens) > 1
+        split = (MIXED_SPLIT_ENABLED and DECODE_CLUSTER_ENABLED and sink is None and 1 in lens and max(lens) > 1
                  and attention_decode_tma_supported(nq, nkv, d, k_cache.shape[2]))
         if split:
             attention_decode_tma(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,
@@ -909,7 +909,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
                                                           all(k >= 2 * n for n, k in zip(lens, kv_lens)))
         n_tiles = n_two if blocks == 2 else n_one
         attention_prefill_tc(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,
-                             step.n_seqs, n_tiles, nq, nkv, d, blocks, skip_single=split)
+                             step.n_seqs, n_tiles, nq, nkv, d, blocks, skip_single=split, sink=sink)
     else:
         n_tiles = sum(-(-n * G // 64) for n in step.h_q_len)
         attention_prefill(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,

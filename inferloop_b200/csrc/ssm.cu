@@ -277,11 +277,14 @@ static int scan_launch(const ScanParams& p, int n_blocks, cudaStream_t stream) {
   if (NPER == 16) ilb::launch(ssm_scan_kernel<TI, 16>, grid, block, smem, stream, p);
   else if (NPER == 32) ilb::launch(ssm_scan_kernel<TI, 32>, grid, block, smem, stream, p);
   else {
+    // four threads a column (a state of up to 256 rows) need more than the default 48 KB: ask once for the most
     static OncePerDevice once;
-    if (once.first() && smem > 48 * 1024 &&
-        cudaFuncSetAttribute(ssm_scan_kernel<TI, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    constexpr size_t kMost = sizeof(float) * ((size_t)2 * kScanTokens * 256 + kScanTokens * kScanCols + 2 * kScanTokens +
+                                             (size_t)kScanTokens * 4 * kScanCols);
+    if (once.first() &&
+        cudaFuncSetAttribute(ssm_scan_kernel<TI, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMost) != cudaSuccess) {
       once.forget();
-      return fail("ssm_scan: cannot reserve %zu bytes of shared memory", smem);
+      return fail("ssm_scan: cannot reserve %zu bytes of shared memory", kMost);
     }
     ilb::launch(ssm_scan_kernel<TI, 64>, grid, block, smem, stream, p);
   }

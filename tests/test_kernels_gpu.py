@@ -295,12 +295,12 @@ def test_kernels_refuse_what_they_cannot_do():
     o = ops()
     with pytest.raises(KernelError, match="CUDA only"):
         o.rmsnorm(torch.randn(2, 8), torch.ones(8), 1e-6, torch.empty(2, 8))
-    q = torch.randn(1, 2 * 272, device="cuda")
-    kc = torch.zeros(2, 1, 16, 272, device="cuda")
+    q = torch.randn(1, 2 * 528, device="cuda")
+    kc = torch.zeros(2, 1, 16, 528, device="cuda")
     with pytest.raises(KernelError, match="head size"):
         o.paged_attention_simple(q, torch.empty_like(q), kc, kc, torch.zeros(1, dtype=torch.int32, device="cuda"),
                                  torch.zeros(1, dtype=torch.int32, device="cuda"),
-                                 torch.zeros(1, 1, dtype=torch.int32, device="cuda"), 0, 1.0, 2, 1, 272)
+                                 torch.zeros(1, 1, dtype=torch.int32, device="cuda"), 0, 1.0, 2, 1, 528)
     with pytest.raises(KernelError, match="multiple"):
         kc = torch.zeros(2, 2, 16, 16, device="cuda")
         q = torch.randn(1, 3 * 16, device="cuda")
