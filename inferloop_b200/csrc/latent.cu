@@ -10,7 +10,7 @@
 //                  into the token's place of its page (dummy rows and released pages are skipped)
 //   head_matmul    out[t, i, :] = x[t, i, :] W[i] for every head i, W [heads, K, N]: the two maps
 //                  above, 16 tokens a block so that a head's matrix is read once per 16 tokens;
-//                  32-bit sums over k in order
+//                  32-bit sums (a step of at most 16 tokens cuts k in four parts that are added in order)
 #include <math.h>
 #include "common.cuh"
 
@@ -60,31 +60,64 @@ ILB_EXPORT int ilb_latent_write(const void* proj, int dtype, int ld, int col0, i
 
 constexpr int kHeadTokens = 16;
 
-template <typename TI, typename TW, typename TO>
+// Block (128 / KS columns n) x (KS ranges of k).  Many tokens: KS = 1, a thread owns a column for 16 tokens.  A step
+// of few tokens has few blocks of that kind, so its k range is cut in four and the parts meet in shared memory.
+template <typename TI, typename TW, typename TO, int KS>
 __global__ void __launch_bounds__(128)
 head_matmul_kernel(const TI* __restrict__ x, int ldx, const TW* __restrict__ w, TO* __restrict__ out, int ldo,
                    int n_tokens, int K, int N) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
-  extern __shared__ __align__(16) float xs[];           // [kHeadTokens][K]
+  constexpr int NT = 128 / KS;
+  extern __shared__ __align__(16) float xs[];           // [kHeadTokens][K], then (KS > 1) [KS][kHeadTokens][NT]
   const int t0 = blockIdx.x * kHeadTokens, h = blockIdx.y;
   const int ts = min(kHeadTokens, n_tokens - t0);
-  for (int i = threadIdx.x; i < kHeadTokens * K; i += blockDim.x) {
+  for (int i = threadIdx.x; i < kHeadTokens * K; i += 128) {
     const int tt = i / K, k = i % K;
     xs[i] = tt < ts ? to_float(x[(size_t)(t0 + tt) * ldx + (size_t)h * K + k]) : 0.f;
   }
   __syncthreads();
-  const int n = blockIdx.z * 128 + threadIdx.x;
-  if (n >= N) return;
+  const int tn = threadIdx.x % NT, tk = threadIdx.x / NT;
+  const int n = blockIdx.z * NT + tn;
+  const bool live = n < N;
+  const int per = ((K + KS - 1) / KS + 3) / 4 * 4;
+  const int k0 = tk * per, k1 = min(K, k0 + per);
   float acc[kHeadTokens];
 #pragma unroll
   for (int tt = 0; tt < kHeadTokens; ++tt) acc[tt] = 0.f;
-  const TW* wp = w + (size_t)h * K * N + n;
-  for (int k = 0; k < K; ++k) {
+  const TW* wp = w + (size_t)h * K * N + (live ? n : 0);
+  int k = k0;
+  if (K % 4 == 0) {
+    for (; k + 4 <= k1; k += 4) {
+      const float w0 = to_float(wp[(size_t)k * N]), w1 = to_float(wp[(size_t)(k + 1) * N]);
+      const float w2 = to_float(wp[(size_t)(k + 2) * N]), w3 = to_float(wp[(size_t)(k + 3) * N]);
+#pragma unroll
+      for (int tt = 0; tt < kHeadTokens; ++tt) {
+        const float4 v = *reinterpret_cast<const float4*>(xs + tt * K + k);
+        acc[tt] = fmaf(v.x, w0, acc[tt]); acc[tt] = fmaf(v.y, w1, acc[tt]);
+        acc[tt] = fmaf(v.z, w2, acc[tt]); acc[tt] = fmaf(v.w, w3, acc[tt]);
+      }
+    }
+  }
+  for (; k < k1; ++k) {
     const float wv = to_float(wp[(size_t)k * N]);
 #pragma unroll
     for (int tt = 0; tt < kHeadTokens; ++tt) acc[tt] = fmaf(xs[tt * K + k], wv, acc[tt]);
   }
+  if (KS > 1) {
+    float* red = xs + kHeadTokens * K;
+#pragma unroll
+    for (int tt = 0; tt < kHeadTokens; ++tt) red[(tk * kHeadTokens + tt) * NT + tn] = acc[tt];
+    __syncthreads();
+    if (tk != 0) return;
+#pragma unroll
+    for (int tt = 0; tt < kHeadTokens; ++tt) {
+      float v = 0.f;
+      for (int r = 0; r < KS; ++r) v += red[(r * kHeadTokens + tt) * NT + tn];
+      acc[tt] = v;
+    }
+  }
+  if (!live) return;
 #pragma unroll
   for (int tt = 0; tt < kHeadTokens; ++tt)
     if (tt < ts) out[(size_t)(t0 + tt) * ldo + (size_t)h * N + n] = from_float<TO>(acc[tt]);
@@ -96,12 +129,19 @@ ILB_EXPORT int ilb_head_matmul(const void* x, int dtype, int ldx, const void* w,
                                int n_tokens, int heads, int K, int N, cudaStream_t stream) {
   ILB_REQUIRE(n_tokens >= 0 && heads > 0 && heads <= 65535 && K > 0 && N > 0, "head_matmul: bad sizes");
   ILB_REQUIRE(ldx >= heads * K && ldo >= heads * N, "head_matmul: strides too small");
-  const size_t smem = sizeof(float) * kHeadTokens * K;
-  ILB_REQUIRE(smem <= 48 * 1024, "head_matmul: inner size %d exceeds %d", K, 48 * 1024 / 4 / kHeadTokens);
+  const bool few = n_tokens <= kHeadTokens;
+  const size_t smem = sizeof(float) * kHeadTokens * ((size_t)K + (few ? 128 : 0));
+  ILB_REQUIRE(smem <= 48 * 1024, "head_matmul: inner size %d exceeds %d", K, 48 * 1024 / 4 / kHeadTokens - 128);
   if (n_tokens == 0) return 0;
-  const dim3 grid((n_tokens + kHeadTokens - 1) / kHeadTokens, heads, (N + 127) / 128);
-#define ILB_HM(TI, TO) ilb::launch(head_matmul_kernel<TI, TI, TO>, grid, dim3(128), smem, stream, (const TI*)x, ldx, (const TI*)w, \
-                                    (TO*)out, ldo, n_tokens, K, N)
+  const int nt = few ? 32 : 128;
+  const dim3 grid((n_tokens + kHeadTokens - 1) / kHeadTokens, heads, (N + nt - 1) / nt);
+#define ILB_HM(TI, TO)                                                                                                        \
+  do {                                                                                                                        \
+    if (few) ilb::launch(head_matmul_kernel<TI, TI, TO, 4>, grid, dim3(128), smem, stream, (const TI*)x, ldx, (const TI*)w,   \
+                         (TO*)out, ldo, n_tokens, K, N);                                                                      \
+    else ilb::launch(head_matmul_kernel<TI, TI, TO, 1>, grid, dim3(128), smem, stream, (const TI*)x, ldx, (const TI*)w,       \
+                     (TO*)out, ldo, n_tokens, K, N);                                                                          \
+  } while (0)
   if (dtype == kF32 && out_dtype == kF32) ILB_HM(float, float);
   else if (dtype == kBF16 && out_dtype == kBF16) ILB_HM(__nv_bfloat16, __nv_bfloat16);
   else if (dtype == kBF16 && out_dtype == kF32) ILB_HM(__nv_bfloat16, float);

@@ -139,8 +139,11 @@ struct ScanParams {
 
 enum : int { kPassWhole = 0, kPassLocal = 1, kPassFinal = 3 };
 
-template <typename TI, int NPER>
-__global__ void __launch_bounds__(256)
+// LOCAL: pass (1), a chunk's own contribution from a zero state, as a plain sum: with w_i the product of the
+// decays after token i up to the end of the staged tokens, S <- (w of them all) S + sum_i (w_i d_i B_i) u_i^T, one
+// fused multiply-add per element of the state and token (B is weighted while it is staged; C is not needed).
+template <typename TI, int NPER, bool LOCAL>
+__global__ void __launch_bounds__(256, 2)
 ssm_scan_kernel(const ScanParams p) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
@@ -150,8 +153,8 @@ ssm_scan_kernel(const ScanParams p) {
   float* Cs = Bs + kScanTokens * NP;                     // [kScanTokens][NP]
   float* us = Cs + kScanTokens * NP;                     // [kScanTokens][kScanCols]
   float* ds = us + kScanTokens * kScanCols;              // [kScanTokens] step sizes
-  float* as = ds + kScanTokens;                          // [kScanTokens] decays
-  float* ys = as + kScanTokens;                          // [kScanTokens][NS][kScanCols], when NS > 1
+  float* as = ds + kScanTokens;                          // [kScanTokens] decays (LOCAL: their logarithms, then the product of all)
+  float* ys = as + kScanTokens + 4;                      // [kScanTokens][NS][kScanCols], when NS > 1
   int seq, ci;
   if (!find_tile(p.cu_q, p.n_seqs, p.chunk, blockIdx.x, seq, ci)) return;
   const int h = blockIdx.y, g = h / (p.heads / p.groups);
@@ -180,23 +183,85 @@ ssm_scan_kernel(const ScanParams p) {
   for (int t0 = begin; t0 < end; t0 += kScanTokens) {
     const int ts = min(kScanTokens, end - t0);
     __syncthreads();
-    for (int i = tid; i < ts * NP; i += n_threads) {
-      const int tt = i / NP, n = i % NP;
-      const float* row = p.act + (size_t)(t0 + tt) * p.channels + inner + (size_t)g * p.N;
-      Bs[i] = n < p.N ? row[n] : 0.f;
-      Cs[i] = n < p.N ? row[(size_t)p.groups * p.N + n] : 0.f;
-    }
-    for (int i = tid; i < ts * kScanCols; i += n_threads) {
-      const int tt = i / kScanCols, c = blockIdx.z * kScanCols + i % kScanCols;
-      us[i] = c < p.P ? p.act[(size_t)(t0 + tt) * p.channels + (size_t)h * p.P + c] : 0.f;
-    }
     if (tid < ts) {
       const float raw = to_float(reinterpret_cast<const TI*>(p.proj)[(size_t)(t0 + tid) * p.ld + p.dt_col0 + h]);
       const float d = softplus_f(raw + bias);
       ds[tid] = d;
-      as[tid] = expf(rate * d);
+      as[tid] = LOCAL ? rate * d : expf(rate * d);
+    }
+    if constexpr (LOCAL) {
+      __syncthreads();
+      float after = 0.f;                                 // logarithm of the decays after this thread's token (<= 0)
+      if (tid < ts) {
+        for (int j = tid + 1; j < ts; ++j) after += as[j];
+        ds[tid] *= expf(after);                          // w_i d_i
+      }
+      if (tid == 0) as[kScanTokens] = expf(after + as[0]);
+      __syncthreads();
+    }
+    // Every load of the group is issued before the first store to shared memory (a load behind a store would
+    // wait for it: the two may alias for all the compiler knows).  n_threads = NS * 64 and NP = NS * NPER: one
+    // round of the block covers 64 / NPER tokens, and a thread keeps its row n through all rounds.
+    {
+      constexpr int kRounds = NPER / 4;                  // kScanTokens / (64 / NPER)
+      constexpr int kPerRound = kScanCols / NPER;        // tokens a round covers
+      const int n = tid % NP, sub = tid / NP;
+      const bool has = n < p.N;
+      const float* base = p.act + inner + (size_t)g * p.N + n;
+      // (three batches, B, C, u, each loaded whole and then stored: a batch is what the registers beside S hold)
+      float r[kRounds];
+#pragma unroll
+      for (int j = 0; j < kRounds; ++j) {
+        const int tt = j * kPerRound + sub;
+        r[j] = (has && tt < ts) ? __ldg(base + (size_t)(t0 + tt) * p.channels) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < kRounds; ++j) {
+        const int tt = j * kPerRound + sub;
+        if constexpr (LOCAL) Bs[tt * NP + n] = tt < ts ? r[j] * ds[tt] : 0.f;
+        else Bs[tt * NP + n] = r[j];
+      }
+      if constexpr (!LOCAL) {
+#pragma unroll
+        for (int j = 0; j < kRounds; ++j) {
+          const int tt = j * kPerRound + sub;
+          r[j] = (has && tt < ts) ? __ldg(base + (size_t)(t0 + tt) * p.channels + (size_t)p.groups * p.N) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < kRounds; ++j) Cs[(j * kPerRound + sub) * NP + n] = r[j];
+      }
+      const int uc = tid % kScanCols, usub = tid / kScanCols;     // usub < NS
+      const int c = blockIdx.z * kScanCols + uc;
+      float ru[kScanTokens];
+#pragma unroll
+      for (int j = 0; j < kScanTokens; ++j) {
+        const int tt = j * NS + usub;
+        ru[j] = (tt < ts && c < p.P) ? __ldg(p.act + (size_t)(t0 + tt) * p.channels + (size_t)h * p.P + c) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < kScanTokens; ++j) {
+        const int tt = j * NS + usub;
+        if (tt < kScanTokens) us[tt * kScanCols + uc] = ru[j];
+      }
     }
     __syncthreads();
+    if constexpr (LOCAL) {
+      const float all = as[kScanTokens];
+#pragma unroll
+      for (int k = 0; k < NPER; ++k) S[k] *= all;
+      for (int tt = 0; tt < ts; ++tt) {
+        const float u = us[tt * kScanCols + tx];
+        const float4* b4 = reinterpret_cast<const float4*>(Bs + tt * NP + ty * NPER);
+#pragma unroll
+        for (int k = 0; k < NPER / 4; ++k) {
+          const float4 b = b4[k];
+          S[4 * k + 0] = fmaf(b.x, u, S[4 * k + 0]); S[4 * k + 1] = fmaf(b.y, u, S[4 * k + 1]);
+          S[4 * k + 2] = fmaf(b.z, u, S[4 * k + 2]); S[4 * k + 3] = fmaf(b.w, u, S[4 * k + 3]);
+        }
+      }
+      decay_all *= all;
+      continue;
+    }
     for (int tt = 0; tt < ts; ++tt) {
       const float u = us[tt * kScanCols + tx], a = as[tt], du = ds[tt] * u;
       const float4* b4 = reinterpret_cast<const float4*>(Bs + tt * NP + ty * NPER);
@@ -271,22 +336,29 @@ static int scan_launch(const ScanParams& p, int n_blocks, cudaStream_t stream) {
   const int NS = (p.N + NPER - 1) / NPER;
   ILB_REQUIRE(NS * kScanCols <= 256, "ssm_scan: a state of %d rows exceeds 256", p.N);
   const int NP = NS * NPER;
-  const size_t smem = sizeof(float) * ((size_t)2 * kScanTokens * NP + kScanTokens * kScanCols + 2 * kScanTokens +
+  const size_t smem = sizeof(float) * ((size_t)2 * kScanTokens * NP + kScanTokens * kScanCols + 2 * kScanTokens + 4 +
                                        (NS > 1 ? (size_t)kScanTokens * NS * kScanCols : 0));
   const dim3 grid(n_blocks, p.heads, (p.P + kScanCols - 1) / kScanCols), block(kScanCols, NS);
-  if (NPER == 16) ilb::launch(ssm_scan_kernel<TI, 16>, grid, block, smem, stream, p);
-  else if (NPER == 32) ilb::launch(ssm_scan_kernel<TI, 32>, grid, block, smem, stream, p);
-  else {
+  const bool local = p.pass == kPassLocal;
+  if (NPER == 16) {
+    if (local) ilb::launch(ssm_scan_kernel<TI, 16, true>, grid, block, smem, stream, p);
+    else ilb::launch(ssm_scan_kernel<TI, 16, false>, grid, block, smem, stream, p);
+  } else if (NPER == 32) {
+    if (local) ilb::launch(ssm_scan_kernel<TI, 32, true>, grid, block, smem, stream, p);
+    else ilb::launch(ssm_scan_kernel<TI, 32, false>, grid, block, smem, stream, p);
+  } else {
     // four threads a column (a state of up to 256 rows) need more than the default 48 KB: ask once for the most
     static OncePerDevice once;
-    constexpr size_t kMost = sizeof(float) * ((size_t)2 * kScanTokens * 256 + kScanTokens * kScanCols + 2 * kScanTokens +
+    constexpr size_t kMost = sizeof(float) * ((size_t)2 * kScanTokens * 256 + kScanTokens * kScanCols + 2 * kScanTokens + 4 +
                                              (size_t)kScanTokens * 4 * kScanCols);
     if (once.first() &&
-        cudaFuncSetAttribute(ssm_scan_kernel<TI, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMost) != cudaSuccess) {
+        (cudaFuncSetAttribute(ssm_scan_kernel<TI, 64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMost) != cudaSuccess ||
+         cudaFuncSetAttribute(ssm_scan_kernel<TI, 64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMost) != cudaSuccess)) {
       once.forget();
       return fail("ssm_scan: cannot reserve %zu bytes of shared memory", kMost);
     }
-    ilb::launch(ssm_scan_kernel<TI, 64>, grid, block, smem, stream, p);
+    if (local) ilb::launch(ssm_scan_kernel<TI, 64, true>, grid, block, smem, stream, p);
+    else ilb::launch(ssm_scan_kernel<TI, 64, false>, grid, block, smem, stream, p);
   }
   return check_launch("ssm_scan");
 }

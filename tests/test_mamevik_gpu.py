@@ -187,7 +187,13 @@ def test_a_long_prompt_whole_and_in_portions(root, name, dtype):
             out = r.step([StepEntry("p", part, [w - at for w in want if at <= w < at + len(part)])])
             rows.append(out.float().cpu().clone())
         r.end("p")
-        assert_close(torch.cat(rows), whole, dtype, f"{name} portions of {portion} against the whole prompt")
+        if dtype == "float32":
+            # two 32-bit evaluations whose recurrences add in another order: what differs is rounding, which a recurrence
+            # over hundreds of tokens amplifies about tenfold; a key outside its window or a lost state differs by percents
+            err = (torch.cat(rows).double() - whole.double()).abs().max()
+            assert err <= 2e-5 * whole.abs().max(), f"{name} portions of {portion}: {float(err):.3e}"
+        else:
+            assert_close(torch.cat(rows), whole, dtype, f"{name} portions of {portion} against the whole prompt")
 
 
 @pytest.mark.parametrize("name,dtype", [("U", "float32"), ("V", "bfloat16"), ("W", "float32")])
