@@ -13,6 +13,7 @@
 //                  32-bit sums (a step of at most 16 tokens cuts k in four parts that are added in order)
 #include <math.h>
 #include "common.cuh"
+#include "sm100.cuh"
 
 using namespace ilb;
 
@@ -123,12 +124,80 @@ head_matmul_kernel(const TI* __restrict__ x, int ldx, const TW* __restrict__ w, 
     if (tt < ts) out[(size_t)(t0 + tt) * ldo + (size_t)h * N + n] = from_float<TO>(acc[tt]);
 }
 
+// The same product for many bfloat16 tokens on the tensor cores (mma.sync m16n8k16, 32-bit sums): a block of four
+// warps takes 64 tokens x 64 columns of one head; the head's matrix passes through shared memory in slices of 64 k
+// ([k][n] as stored, read with ldmatrix.trans), the tokens' rows come straight from global memory as A fragments.
+// K a multiple of 16, N of 8.
+constexpr int kMmaTile = 64;
+
+__global__ void __launch_bounds__(128)
+head_matmul_mma_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ w,
+                       __nv_bfloat16* __restrict__ out, int ldo, int n_tokens, int K, int N) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  __shared__ __align__(16) __nv_bfloat16 ws[kMmaTile][kMmaTile + 8];
+  const int t0 = blockIdx.x * kMmaTile, h = blockIdx.y, n0 = blockIdx.z * kMmaTile;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int r0 = t0 + warp * 16 + g, r1 = r0 + 8;
+  const bool live0 = r0 < n_tokens, live1 = r1 < n_tokens;
+  const __nv_bfloat16* a0 = x + (size_t)(live0 ? r0 : 0) * ldx + (size_t)h * K;
+  const __nv_bfloat16* a1 = x + (size_t)(live1 ? r1 : 0) * ldx + (size_t)h * K;
+  float acc[kMmaTile / 8][4];
+#pragma unroll
+  for (int i = 0; i < kMmaTile / 8; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[i][e] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += kMmaTile) {
+    __syncthreads();
+#pragma unroll
+    for (int it = 0; it < kMmaTile * (kMmaTile / 8) / 128; ++it) {
+      const int idx = threadIdx.x + it * 128, r = idx / (kMmaTile / 8), cv = idx % (kMmaTile / 8);
+      const int k = k0 + r, n = n0 + cv * 8;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (k < K && n < N) v = __ldg(reinterpret_cast<const uint4*>(w + ((size_t)h * K + k) * N + n));
+      *reinterpret_cast<uint4*>(&ws[r][cv * 8]) = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kb = 0; kb < kMmaTile / 16; ++kb) {
+      const int c = k0 + kb * 16 + 2 * t;
+      if (k0 + kb * 16 >= K) break;
+      uint32_t a[4];
+      a[0] = live0 ? *reinterpret_cast<const uint32_t*>(a0 + c) : 0u;
+      a[1] = live1 ? *reinterpret_cast<const uint32_t*>(a1 + c) : 0u;
+      a[2] = live0 ? *reinterpret_cast<const uint32_t*>(a0 + c + 8) : 0u;
+      a[3] = live1 ? *reinterpret_cast<const uint32_t*>(a1 + c + 8) : 0u;
+#pragma unroll
+      for (int nd = 0; nd < kMmaTile / 16; ++nd) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(smem_u32(&ws[kb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][nd * 16 + (lane >> 4) * 8]), b0, b1, b2, b3);
+        mma_16816(acc[2 * nd], a, b0, b1);
+        mma_16816(acc[2 * nd + 1], a, b2, b3);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kMmaTile / 8; ++i) {
+    const int col = n0 + i * 8 + 2 * t;
+    if (col >= N) continue;
+    if (live0) *reinterpret_cast<uint32_t*>(out + (size_t)r0 * ldo + (size_t)h * N + col) = pack_bf16(acc[i][0], acc[i][1]);
+    if (live1) *reinterpret_cast<uint32_t*>(out + (size_t)r1 * ldo + (size_t)h * N + col) = pack_bf16(acc[i][2], acc[i][3]);
+  }
+}
+
 // x: [T, ldx] of `dtype`, head i at columns i * K ..; w: [heads, K, N] of `dtype`; out: [T, ldo] of
 // `out_dtype`, head i at columns i * N ...
 ILB_EXPORT int ilb_head_matmul(const void* x, int dtype, int ldx, const void* w, void* out, int out_dtype, int ldo,
                                int n_tokens, int heads, int K, int N, cudaStream_t stream) {
   ILB_REQUIRE(n_tokens >= 0 && heads > 0 && heads <= 65535 && K > 0 && N > 0, "head_matmul: bad sizes");
   ILB_REQUIRE(ldx >= heads * K && ldo >= heads * N, "head_matmul: strides too small");
+  if (dtype == kBF16 && out_dtype == kBF16 && n_tokens > kHeadTokens && K % 16 == 0 && N % 8 == 0 && ldx % 2 == 0 && ldo % 2 == 0 &&
+      ((uintptr_t)x % 4 == 0) && ((uintptr_t)out % 4 == 0) && ((uintptr_t)w % 16 == 0)) {
+    const dim3 grid((n_tokens + kMmaTile - 1) / kMmaTile, heads, (N + kMmaTile - 1) / kMmaTile);
+    ilb::launch(head_matmul_mma_kernel, grid, dim3(128), 0, stream, (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w,
+                (__nv_bfloat16*)out, ldo, n_tokens, K, N);
+    return check_launch("head_matmul");
+  }
   const bool few = n_tokens <= kHeadTokens;
   const size_t smem = sizeof(float) * kHeadTokens * ((size_t)K + (few ? 128 : 0));
   ILB_REQUIRE(smem <= 48 * 1024, "head_matmul: inner size %d exceeds %d", K, 48 * 1024 / 4 / kHeadTokens - 128);

@@ -206,7 +206,14 @@ def ssm_scan(act: torch.Tensor, proj: torch.Tensor, dt_col0: int, dt_bias: torch
             or tuple(state.shape[1:]) != (heads, n_state, head_dim):
         raise KernelError("ssm_scan: shapes do not agree")
     if chunk is None:
-        chunk = SSM_CHUNK if step.max_q_len >= SSM_CHUNK_FROM else 0
+        chunk = 0
+        if step.max_q_len >= SSM_CHUNK_FROM:
+            # chunks of 64, 128 or 256 tokens: the launch runs in rounds of about four blocks an SM, a round takes as
+            # long as a chunk, and of equal products the longer chunk wins (fewer states to carry)
+            room = 4 * _sm_count(act.device)
+            tiles = heads * -(-head_dim // 64)
+            cost = lambda c: -(-(sum(-(-n // c) for n in step.h_q_len) * tiles) // room) * c
+            chunk = min((SSM_CHUNK, 2 * SSM_CHUNK, 4 * SSM_CHUNK), key=lambda c: (cost(c), -c))
     chunk_state = chunk_decay = None
     n_blocks = step.n_seqs
     if chunk:
@@ -239,6 +246,8 @@ def latent_write(proj: torch.Tensor, col0: int, rank: int, weight: torch.Tensor,
     _need(block_table, "block table", torch.int32)
     if cache.dim() != 4 or cache.shape[1] != 1 or cache.shape[3] != rank or weight.numel() != rank:
         raise KernelError("latent_write: cache must be [pages, 1, page_size, rank]")
+    if proj.shape[0] != step.n_tokens:
+        raise KernelError(f"latent_write: {proj.shape[0]} rows for a step of {step.n_tokens} tokens")
     _call("latent", "ilb_latent_write", _ptr(proj), _i(_code(proj)), _i(proj.stride(0)), _i(col0), _i(rank), _ptr(weight), _f(eps),
           _ptr(step.positions), _ptr(step.seq_of_token), _ptr(block_table), _i(block_table.shape[1]), _i(cache.shape[2]),
           _i(cache.shape[0]), _ptr(cache), _i(_code(cache)), _i(proj.shape[0]), _stream(cache))

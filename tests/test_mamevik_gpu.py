@@ -451,16 +451,17 @@ def test_attention_with_a_sink_and_a_window_over_cached_latents(dtype, rank, hea
 def test_products_per_head_and_the_latent_write(dtype, heads, K, N):
     from inferloop_b200.csrc import ops
     g = torch.Generator().manual_seed(heads + K + N)
-    T = 37
-    x = torch.randn(T, heads * K + 11, generator=g).to(dtype)
+    x = torch.randn(150, heads * K + (12 if K % 16 == 0 else 11), generator=g).to(dtype)     # (even row strides reach the tensor-core form)
     w = (torch.randn(heads, K, N, generator=g) / math.sqrt(K)).to(dtype)
-    out = torch.empty(T, heads * N, dtype=dtype, device=DEV)
-    ops.head_matmul(x.to(DEV), w.to(DEV), out)
-    ref = torch.einsum("thk,hkn->thn", x.double()[:, :heads * K].reshape(T, heads, K), w.double()).reshape(T, heads * N)
-    if dtype == torch.float32:
-        assert_close(out, ref, "float32", "per-head product")
-    else:
-        assert (out.double().cpu() - ref).abs().max() <= 2.0 ** -8 * ref.abs().max()
+    for T in (150, 37, 16, 3):                # many tokens, and the few-token form whose k range is cut in four
+        out = torch.empty(T, heads * N, dtype=dtype, device=DEV)
+        ops.head_matmul(x[:T].to(DEV), w.to(DEV), out)
+        ref = torch.einsum("thk,hkn->thn", x.double()[:T, :heads * K].reshape(T, heads, K), w.double()).reshape(T, heads * N)
+        if dtype == torch.float32:
+            assert_close(out, ref, "float32", f"per-head product of {T} tokens")
+        else:
+            assert (out.double().cpu() - ref).abs().max() <= 2.0 ** -8 * ref.abs().max()
+    T = 37
     # the latent: columns heads * K - 5 .. of x, normed, into pages out of order; a dummy row (no page) is dropped
     rank, page = 16, 4
     gw = 1 + 0.1 * torch.randn(rank, generator=g)
@@ -468,8 +469,8 @@ def test_products_per_head_and_the_latent_write(dtype, heads, K, N):
     step = FakeStep([30, 6, 1], [3, 0, 0], [0, 1, -1])
     table = torch.tensor([[5, 9, 2, 7, 0, 1, 3, 4, 6], [11, 10] + [-1] * 7, [-1] * 9], dtype=torch.int32, device=DEV)
     col0 = heads * K - 5
-    ops.latent_write(x.to(DEV), col0, rank, f32(gw), 1e-5, step, table, cache)
-    want = plain.rms(x.double()[:, col0:col0 + rank], 1e-5) * gw.double()
+    ops.latent_write(x[:T].to(DEV), col0, rank, f32(gw), 1e-5, step, table, cache)
+    want = plain.rms(x.double()[:T, col0:col0 + rank], 1e-5) * gw.double()
     for t, (seq, pos) in enumerate([(0, 3 + i) for i in range(30)] + [(1, i) for i in range(6)]):
         got = cache[int(table[seq, pos // page]), 0, pos % page].double().cpu()
         assert (got - want[t]).abs().max() <= (1e-5 if dtype == torch.float32 else 2.0 ** -8 * float(want[t].abs().max()))
