@@ -335,7 +335,7 @@ decode_kernel(const DecodeParams p) {
   float* merge = reinterpret_cast<float*>(smem_raw);                  // reused once the tiles are consumed
   __shared__ int s_last;
   const int G = p.nq / p.cache.nkv;
-  const int kvh = blockIdx.x, seq = blockIdx.y, chunk_i = blockIdx.z;
+  const int kvh = blockIdx.x, seq = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int tok = p.cu_q[seq];
   if (p.cu_q[seq + 1] - tok != 1) return;          // decode handles one token per sequence
@@ -343,7 +343,10 @@ decode_kernel(const DecodeParams p) {
   const int lo = (p.window > 0 && pos + 1 > p.window) ? pos + 1 - p.window : 0;
   const int hi = pos + 1;
   const int c_lo = lo / p.chunk, c_hi = pos / p.chunk;
-  if (chunk_i < c_lo || chunk_i > c_hi) return;
+  // the grid's third index counts from the first chunk this token reads: with a window the records of a
+  // sequence are as many as a window touches, wherever in the sequence it lies
+  const int rel_i = blockIdx.z, chunk_i = c_lo + rel_i;
+  if (chunk_i > c_hi) return;
   const int n_chunks = c_hi - c_lo + 1;
   const int* table = p.block_table + (size_t)seq * p.max_blocks;
   const int key_begin = chunk_i * p.chunk;
@@ -399,7 +402,7 @@ decode_kernel(const DecodeParams p) {
       if (t == 0) { row[D] = st.m[r]; row[D + 1] = l; }
     }
     __syncthreads();
-    float* rec = rec_base + ((size_t)chunk_i * G + rb) * kRec;
+    float* rec = rec_base + ((size_t)rel_i * G + rb) * kRec;
     const int live_rows = min(16, G - rb);
     for (int idx = threadIdx.x; idx < live_rows * kRec; idx += kWarps * 32) {
       const int row = idx / kRec, c = idx % kRec;
@@ -424,7 +427,7 @@ decode_kernel(const DecodeParams p) {
     __threadfence_block();
     for (int idx = threadIdx.x; idx < G * D; idx += kWarps * 32) {
       const int h = idx / D, c = idx % D;
-      const float* rec = rec_base + ((size_t)chunk_i * G + h) * kRec;
+      const float* rec = rec_base + ((size_t)rel_i * G + h) * kRec;
       float l = rec[D + 1];
       if (p.sink != nullptr && rec[D] != -INFINITY) l += exp2f(p.sink[kvh * G + h] * kLog2e - rec[D]);
       p.out[(size_t)tok * p.out_stride + (size_t)(kvh * G + h) * D + c] = __float2bfloat16_rn(l > 0.f ? rec[c] / l : 0.f);
@@ -452,7 +455,7 @@ decode_kernel(const DecodeParams p) {
     float m_all = -INFINITY;
     for (int c0 = 0; c0 < n_chunks; c0 += 32) {
       const int ci = c0 + lane;
-      const float mc = ci < n_chunks ? __ldcg(rec_base + ((size_t)(c_lo + ci) * G + h) * kRec + D) : -INFINITY;
+      const float mc = ci < n_chunks ? __ldcg(rec_base + ((size_t)ci * G + h) * kRec + D) : -INFINITY;
       m_all = fmaxf(m_all, mc);
     }
 #pragma unroll
@@ -462,7 +465,7 @@ decode_kernel(const DecodeParams p) {
       const int ci = c0 + lane;
       float f = 0.f, l = 0.f;
       if (ci < n_chunks) {
-        const float* rec = rec_base + ((size_t)(c_lo + ci) * G + h) * kRec;
+        const float* rec = rec_base + ((size_t)ci * G + h) * kRec;
         const float mc = __ldcg(rec + D);
         l = __ldcg(rec + D + 1);
         f = (mc == -INFINITY) ? 0.f : exp2f(mc - m_all);
@@ -493,7 +496,7 @@ decode_kernel(const DecodeParams p) {
         const int h = idx / D, c = idx % D;
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-          v[e][j] = (idx < G * D && c0 + j < n_chunks) ? __ldcg(rec_base + ((size_t)(c_lo + c0 + j) * G + h) * kRec + c) : 0.f;
+          v[e][j] = (idx < G * D && c0 + j < n_chunks) ? __ldcg(rec_base + ((size_t)(c0 + j) * G + h) * kRec + c) : 0.f;
       }
 #pragma unroll
       for (int e = 0; e < kPerThread; ++e) {
@@ -590,7 +593,9 @@ ILB_EXPORT int ilb_attention_decode(const void* q, void* out, const void* k_cach
   // Every key the block tables can name must fall into one of the chunks: a sequence longer
   // than max_chunks * chunk would wait for chunks that the grid does not hold, and its row
   // would never be written.
-  ILB_REQUIRE((long long)max_chunks * chunk >= (long long)max_blocks * page_size,
+  // (With a window a token reads at most (window - 1) / chunk + 2 chunks, and the grid counts from its first.)
+  ILB_REQUIRE((long long)max_chunks * chunk >= (long long)max_blocks * page_size ||
+              (window > 0 && max_chunks >= (window - 1) / chunk + 2),
               "attention decode: %d chunks of %d keys do not cover the %d x %d keys the block tables can name",
               max_chunks, chunk, max_blocks, page_size);
   // The last chunk's merge keeps one weight per (head of the group, chunk) in the shared

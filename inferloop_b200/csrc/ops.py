@@ -895,6 +895,8 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
         page_size = k_cache.shape[2]
         capacity = block_table.shape[1] * page_size
         max_chunks = max(1, -(-capacity // decode_chunk))
+        if window:                       # a token reads the chunks its window touches, counted from the first of them
+            max_chunks = min(max_chunks, (window - 1) // decode_chunk + 2)
         scratch = workspace.buffer("attn.decode_scratch", (step.n_seqs * nkv * max_chunks * G * (d + 2),), torch.float32)
         tickets = workspace.zeroed("attn.decode_tickets", (max(step.n_seqs * nkv, 4096),), torch.int32)
         attention_decode(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,

@@ -39,7 +39,9 @@ class LatentAttention(Mixer):
         self.window = spec.get("window")
         self.has_sink = bool(spec.get("sink", False))
         self.eps = float(spec["eps"])
-        self.decode_chunk = ops.decode_chunk_for(int(spec.get("max_positions", 4096)))
+        # split-KV decode cuts the keys at multiples of this, fixed per model; with a window the chunks a token reads
+        # are few wherever it stands, so they can be short
+        self.decode_chunk = ops.DECODE_CHUNK_MIN if self.window else ops.decode_chunk_for(int(spec.get("max_positions", 4096)))
         names = {"q": "q", "down": "dkv", "down_norm": "dkv.norm", "up_k": "uk", "up_v": "uv", "sink": "sink", "o": "o"}
         for role, name in spec.get("names", ()):
             if role not in names:
