@@ -52,6 +52,8 @@ class StateSpaceMixer:
             raise ConfigError(f"config.json: {what}: heads * vdim is not a multiple of norm_groups")
         if out.conv > 16:
             raise UnsupportedConfig(f"config.json: {what}.conv: more than 16 taps are not served")
+        if out.state > 256:
+            raise UnsupportedConfig(f"config.json: {what}.state: more than 256 rows of state are not served")
         return out
 
 
@@ -69,8 +71,11 @@ class LatentAttentionMixer:
         d = _obj(d, what)
         mask = d.get("mask")
         window = None if mask is None else _int(_obj(mask, what + ".mask"), "size", what + ".mask")
-        return cls(_int(d, "heads", what), _int(d, "dim", what), _int(d, "vdim", what), _int(d, "kv_rank", what),
-                   _num(d, "scale", what), window)
+        out = cls(_int(d, "heads", what), _int(d, "dim", what), _int(d, "vdim", what), _int(d, "kv_rank", what),
+                  _num(d, "scale", what), window)
+        if max(out.kv_rank, out.dim, out.vdim) > 512:
+            raise UnsupportedConfig(f"config.json: {what}: kv_rank, dim and vdim beyond 512 are not served")
+        return out
 
 
 @dataclass(frozen=True)
@@ -93,6 +98,8 @@ class ExpertsFeedForward:
             raise ConfigError(f"config.json: {what}.router: top {out.top} of {out.experts} experts")
         if out.limit <= 0:
             raise ConfigError(f"config.json: {what}.expert.limit must be positive")
+        if out.experts > 512 or out.top > 32:
+            raise UnsupportedConfig(f"config.json: {what}.router: more than 512 experts or 32 a token are not served")
         return out
 
 

@@ -139,9 +139,24 @@ struct ScanParams {
 
 enum : int { kPassWhole = 0, kPassLocal = 1, kPassFinal = 3 };
 
+__device__ __forceinline__ void cp_async_4(float* dst, const float* src, bool ok) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(src), "r"(ok ? 4 : 0) : "memory");      // (0 bytes read: zeros)
+}
+__device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Floats of shared memory a block of NS threads a column needs: two buffers of (B, C, u) of 16 tokens, their step
+// sizes and decays, and the partial outputs of the NS threads of a column.
+static inline size_t scan_smem_floats(int NP, int NS) {
+  return (size_t)2 * (2 * kScanTokens * NP + kScanTokens * kScanCols) + 2 * kScanTokens + 2 * (kScanTokens + 4) +
+         (NS > 1 ? (size_t)kScanTokens * NS * kScanCols : 0);
+}
+
+// The tokens are staged 16 at a time by asynchronous copies, a group ahead of the arithmetic.
 // LOCAL: pass (1), a chunk's own contribution from a zero state, as a plain sum: with w_i the product of the
-// decays after token i up to the end of the staged tokens, S <- (w of them all) S + sum_i (w_i d_i B_i) u_i^T, one
-// fused multiply-add per element of the state and token (B is weighted while it is staged; C is not needed).
+// decays after token i up to the end of the staged tokens, S <- (w of them all) S + sum_i B_i (w_i d_i u_i)^T, one
+// fused multiply-add per element of the state and token (C is not needed).
 template <typename TI, int NPER, bool LOCAL>
 __global__ void __launch_bounds__(256, 2)
 ssm_scan_kernel(const ScanParams p) {
@@ -149,12 +164,10 @@ ssm_scan_kernel(const ScanParams p) {
   ilb::pdl_wait();
   extern __shared__ __align__(16) float smem[];
   const int NS = blockDim.y, NP = NS * NPER;            // NP >= N, rows beyond N are zero
-  float* Bs = smem;                                      // [kScanTokens][NP]
-  float* Cs = Bs + kScanTokens * NP;                     // [kScanTokens][NP]
-  float* us = Cs + kScanTokens * NP;                     // [kScanTokens][kScanCols]
-  float* ds = us + kScanTokens * kScanCols;              // [kScanTokens] step sizes
-  float* as = ds + kScanTokens;                          // [kScanTokens] decays (LOCAL: their logarithms, then the product of all)
-  float* ys = as + kScanTokens + 4;                      // [kScanTokens][NS][kScanCols], when NS > 1
+  const int kBuf = 2 * kScanTokens * NP + kScanTokens * kScanCols;     // floats of one buffer: B, C, u
+  float* ds = smem + 2 * kBuf;                           // [2][kScanTokens] step sizes (LOCAL: then w_i d_i)
+  float* as = ds + 2 * kScanTokens;                      // [2][kScanTokens + 4] decays (LOCAL: their logarithms, then the product of all)
+  float* ys = as + 2 * (kScanTokens + 4);                // [kScanTokens][NS][kScanCols], when NS > 1
   int seq, ci;
   if (!find_tile(p.cu_q, p.n_seqs, p.chunk, blockIdx.x, seq, ci)) return;
   const int h = blockIdx.y, g = h / (p.heads / p.groups);
@@ -179,78 +192,79 @@ ssm_scan_kernel(const ScanParams p) {
       S[k] = (src != nullptr && live && n < p.N) ? src[(size_t)n * p.P + col] : 0.f;
     }
   }
-  float decay_all = 1.f;
-  for (int t0 = begin; t0 < end; t0 += kScanTokens) {
-    const int ts = min(kScanTokens, end - t0);
-    __syncthreads();
-    if (tid < ts) {
-      const float raw = to_float(reinterpret_cast<const TI*>(p.proj)[(size_t)(t0 + tid) * p.ld + p.dt_col0 + h]);
-      const float d = softplus_f(raw + bias);
-      ds[tid] = d;
-      as[tid] = LOCAL ? rate * d : expf(rate * d);
+  // n_threads = NS * 64 and NP = NS * NPER: one round of the block covers 64 / NPER tokens of B (and C), and a
+  // thread keeps its row n through all rounds; u: a round covers NS tokens.
+  constexpr int kRounds = NPER / 4;                    // kScanTokens / (64 / NPER)
+  constexpr int kPerRound = kScanCols / NPER;
+  const int bn = tid % NP, bsub = tid / NP;
+  const bool has = bn < p.N;
+  const float* bbase = p.act + inner + (size_t)g * p.N + (has ? bn : 0);
+  const int uc = tid % kScanCols, usub = tid / kScanCols;
+  const bool ulive = blockIdx.z * kScanCols + uc < p.P;
+  const float* ubase = p.act + (size_t)h * p.P + (ulive ? blockIdx.z * kScanCols + uc : 0);
+  auto issue = [&](int t0n, int buf) {
+    const int tsn = min(kScanTokens, end - t0n);
+    float* Bb = smem + buf * kBuf;
+    float* Cb = Bb + kScanTokens * NP;
+    float* ub = Cb + kScanTokens * NP;
+#pragma unroll
+    for (int j = 0; j < kRounds; ++j) {
+      const int tt = j * kPerRound + bsub;
+      const bool ok = has && tt < tsn;
+      const float* at = bbase + (size_t)(t0n + (ok ? tt : 0)) * p.channels;
+      cp_async_4(Bb + tt * NP + bn, at, ok);
+      if constexpr (!LOCAL) cp_async_4(Cb + tt * NP + bn, at + (size_t)p.groups * p.N, ok);
     }
+#pragma unroll
+    for (int j = 0; j < kScanTokens; ++j) {
+      const int tt = j * NS + usub;
+      if (tt < kScanTokens) {
+        const bool ok = ulive && tt < tsn;
+        cp_async_4(ub + tt * kScanCols + uc, ubase + (size_t)(t0n + (ok ? tt : 0)) * p.channels, ok);
+      }
+    }
+    cp_async_commit_group();
+  };
+  auto raw_step = [&](int t0n) {
+    return tid < min(kScanTokens, end - t0n) ? to_float(reinterpret_cast<const TI*>(p.proj)[(size_t)(t0n + tid) * p.ld + p.dt_col0 + h]) : 0.f;
+  };
+  float decay_all = 1.f;
+  float raw = begin < end ? raw_step(begin) : 0.f;
+  if (begin < end) issue(begin, 0);
+  int buf = 0;
+  for (int t0 = begin; t0 < end; t0 += kScanTokens, buf ^= 1) {
+    const int ts = min(kScanTokens, end - t0);
+    const float* Bs = smem + buf * kBuf;
+    const float* Cs = Bs + kScanTokens * NP;
+    const float* us = Cs + kScanTokens * NP;
+    float* dsb = ds + buf * kScanTokens;
+    float* asb = as + buf * (kScanTokens + 4);
+    if (tid < ts) {
+      const float d = softplus_f(raw + bias);
+      dsb[tid] = d;
+      asb[tid] = LOCAL ? rate * d : expf(rate * d);
+    }
+    if (t0 + kScanTokens < end) {
+      raw = raw_step(t0 + kScanTokens);
+      issue(t0 + kScanTokens, buf ^ 1);
+      cp_async_wait_group<1>();
+    } else {
+      cp_async_wait_group<0>();
+    }
+    __syncthreads();                                     // this group's B, C, u, step sizes and decays are in place
     if constexpr (LOCAL) {
-      __syncthreads();
       float after = 0.f;                                 // logarithm of the decays after this thread's token (<= 0)
       if (tid < ts) {
-        for (int j = tid + 1; j < ts; ++j) after += as[j];
-        ds[tid] *= expf(after);                          // w_i d_i
+        for (int j = tid + 1; j < ts; ++j) after += asb[j];
+        dsb[tid] *= expf(after);                         // w_i d_i
       }
-      if (tid == 0) as[kScanTokens] = expf(after + as[0]);
+      if (tid == 0) asb[kScanTokens] = expf(after + asb[0]);
       __syncthreads();
-    }
-    // Every load of the group is issued before the first store to shared memory (a load behind a store would
-    // wait for it: the two may alias for all the compiler knows).  n_threads = NS * 64 and NP = NS * NPER: one
-    // round of the block covers 64 / NPER tokens, and a thread keeps its row n through all rounds.
-    {
-      constexpr int kRounds = NPER / 4;                  // kScanTokens / (64 / NPER)
-      constexpr int kPerRound = kScanCols / NPER;        // tokens a round covers
-      const int n = tid % NP, sub = tid / NP;
-      const bool has = n < p.N;
-      const float* base = p.act + inner + (size_t)g * p.N + n;
-      // (three batches, B, C, u, each loaded whole and then stored: a batch is what the registers beside S hold)
-      float r[kRounds];
-#pragma unroll
-      for (int j = 0; j < kRounds; ++j) {
-        const int tt = j * kPerRound + sub;
-        r[j] = (has && tt < ts) ? __ldg(base + (size_t)(t0 + tt) * p.channels) : 0.f;
-      }
-#pragma unroll
-      for (int j = 0; j < kRounds; ++j) {
-        const int tt = j * kPerRound + sub;
-        if constexpr (LOCAL) Bs[tt * NP + n] = tt < ts ? r[j] * ds[tt] : 0.f;
-        else Bs[tt * NP + n] = r[j];
-      }
-      if constexpr (!LOCAL) {
-#pragma unroll
-        for (int j = 0; j < kRounds; ++j) {
-          const int tt = j * kPerRound + sub;
-          r[j] = (has && tt < ts) ? __ldg(base + (size_t)(t0 + tt) * p.channels + (size_t)p.groups * p.N) : 0.f;
-        }
-#pragma unroll
-        for (int j = 0; j < kRounds; ++j) Cs[(j * kPerRound + sub) * NP + n] = r[j];
-      }
-      const int uc = tid % kScanCols, usub = tid / kScanCols;     // usub < NS
-      const int c = blockIdx.z * kScanCols + uc;
-      float ru[kScanTokens];
-#pragma unroll
-      for (int j = 0; j < kScanTokens; ++j) {
-        const int tt = j * NS + usub;
-        ru[j] = (tt < ts && c < p.P) ? __ldg(p.act + (size_t)(t0 + tt) * p.channels + (size_t)h * p.P + c) : 0.f;
-      }
-#pragma unroll
-      for (int j = 0; j < kScanTokens; ++j) {
-        const int tt = j * NS + usub;
-        if (tt < kScanTokens) us[tt * kScanCols + uc] = ru[j];
-      }
-    }
-    __syncthreads();
-    if constexpr (LOCAL) {
-      const float all = as[kScanTokens];
+      const float all = asb[kScanTokens];
 #pragma unroll
       for (int k = 0; k < NPER; ++k) S[k] *= all;
       for (int tt = 0; tt < ts; ++tt) {
-        const float u = us[tt * kScanCols + tx];
+        const float u = us[tt * kScanCols + tx] * dsb[tt];
         const float4* b4 = reinterpret_cast<const float4*>(Bs + tt * NP + ty * NPER);
 #pragma unroll
         for (int k = 0; k < NPER / 4; ++k) {
@@ -260,37 +274,37 @@ ssm_scan_kernel(const ScanParams p) {
         }
       }
       decay_all *= all;
-      continue;
-    }
-    for (int tt = 0; tt < ts; ++tt) {
-      const float u = us[tt * kScanCols + tx], a = as[tt], du = ds[tt] * u;
-      const float4* b4 = reinterpret_cast<const float4*>(Bs + tt * NP + ty * NPER);
-      const float4* c4 = reinterpret_cast<const float4*>(Cs + tt * NP + ty * NPER);
-      float acc = 0.f;
+    } else {
+      for (int tt = 0; tt < ts; ++tt) {
+        const float u = us[tt * kScanCols + tx], a = asb[tt], du = dsb[tt] * u;
+        const float4* b4 = reinterpret_cast<const float4*>(Bs + tt * NP + ty * NPER);
+        const float4* c4 = reinterpret_cast<const float4*>(Cs + tt * NP + ty * NPER);
+        float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;        // four chains: a sum of NPER terms does not wait on itself
 #pragma unroll
-      for (int k = 0; k < NPER / 4; ++k) {
-        const float4 b = b4[k], c = c4[k];
-        S[4 * k + 0] = fmaf(a, S[4 * k + 0], b.x * du); acc = fmaf(S[4 * k + 0], c.x, acc);
-        S[4 * k + 1] = fmaf(a, S[4 * k + 1], b.y * du); acc = fmaf(S[4 * k + 1], c.y, acc);
-        S[4 * k + 2] = fmaf(a, S[4 * k + 2], b.z * du); acc = fmaf(S[4 * k + 2], c.z, acc);
-        S[4 * k + 3] = fmaf(a, S[4 * k + 3], b.w * du); acc = fmaf(S[4 * k + 3], c.w, acc);
-      }
-      decay_all *= a;
-      if (p.pass != kPassLocal) {
+        for (int k = 0; k < NPER / 4; ++k) {
+          const float4 b = b4[k], c = c4[k];
+          S[4 * k + 0] = fmaf(a, S[4 * k + 0], b.x * du); acc0 = fmaf(S[4 * k + 0], c.x, acc0);
+          S[4 * k + 1] = fmaf(a, S[4 * k + 1], b.y * du); acc1 = fmaf(S[4 * k + 1], c.y, acc1);
+          S[4 * k + 2] = fmaf(a, S[4 * k + 2], b.z * du); acc2 = fmaf(S[4 * k + 2], c.z, acc2);
+          S[4 * k + 3] = fmaf(a, S[4 * k + 3], b.w * du); acc3 = fmaf(S[4 * k + 3], c.w, acc3);
+        }
+        const float acc = (acc0 + acc1) + (acc2 + acc3);
+        decay_all *= a;
         if (NS == 1) { if (live) p.y[(size_t)(t0 + tt) * inner + (size_t)h * p.P + col] = fmaf(skip, u, acc); }
         else ys[(tt * NS + ty) * kScanCols + tx] = acc;
       }
-    }
-    if (NS > 1 && p.pass != kPassLocal) {
-      __syncthreads();
-      for (int i = tid; i < ts * kScanCols; i += n_threads) {
-        const int tt = i / kScanCols, x = i % kScanCols, c = blockIdx.z * kScanCols + x;
-        if (c >= p.P) continue;
-        float acc = 0.f;
-        for (int s = 0; s < NS; ++s) acc += ys[(tt * NS + s) * kScanCols + x];
-        p.y[(size_t)(t0 + tt) * inner + (size_t)h * p.P + c] = fmaf(skip, us[tt * kScanCols + x], acc);
+      if (NS > 1) {
+        __syncthreads();
+        for (int i = tid; i < ts * kScanCols; i += n_threads) {
+          const int tt = i / kScanCols, x = i % kScanCols, c = blockIdx.z * kScanCols + x;
+          if (c >= p.P) continue;
+          float acc = 0.f;
+          for (int s = 0; s < NS; ++s) acc += ys[(tt * NS + s) * kScanCols + x];
+          p.y[(size_t)(t0 + tt) * inner + (size_t)h * p.P + c] = fmaf(skip, us[tt * kScanCols + x], acc);
+        }
       }
     }
+    __syncthreads();                                     // everyone is done with this buffer: the next round's copies may overwrite it
   }
   float* dst = nullptr;
   if (p.pass == kPassWhole) { if (slot >= 0) dst = p.state + ((size_t)slot * p.heads + h) * per_head; }
@@ -332,14 +346,29 @@ ssm_carry_kernel(float* __restrict__ state, float* __restrict__ chunk_state, con
 
 template <typename TI>
 static int scan_launch(const ScanParams& p, int n_blocks, cudaStream_t stream) {
-  const int NPER = p.N <= 16 ? 16 : (p.N <= 32 ? 32 : 64);
+  static const int forced = getenv("ILB_SSM_ROWS") ? atoi(getenv("ILB_SSM_ROWS")) : 0;      // measurements: rows a thread holds
+  int NPER = p.N <= 16 ? 16 : (p.N <= 32 ? 32 : 64);
+  if ((forced == 16 || forced == 32 || forced == 64) && (p.N + forced - 1) / forced * kScanCols <= 256) NPER = forced;
   const int NS = (p.N + NPER - 1) / NPER;
   ILB_REQUIRE(NS * kScanCols <= 256, "ssm_scan: a state of %d rows exceeds 256", p.N);
   const int NP = NS * NPER;
-  const size_t smem = sizeof(float) * ((size_t)2 * kScanTokens * NP + kScanTokens * kScanCols + 2 * kScanTokens + 4 +
-                                       (NS > 1 ? (size_t)kScanTokens * NS * kScanCols : 0));
+  const size_t smem = sizeof(float) * scan_smem_floats(NP, NS);
   const dim3 grid(n_blocks, p.heads, (p.P + kScanCols - 1) / kScanCols), block(kScanCols, NS);
   const bool local = p.pass == kPassLocal;
+  // several threads a column (a state of more than 64 rows) need more than the default 48 KB: ask once for the most
+  static OncePerDevice once;
+  if (once.first()) {
+    const int most = (int)(sizeof(float) * scan_smem_floats(256, 4));
+    bool ok = true;
+    ok = ok && cudaFuncSetAttribute(ssm_scan_kernel<TI, 32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) == cudaSuccess;
+    ok = ok && cudaFuncSetAttribute(ssm_scan_kernel<TI, 32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) == cudaSuccess;
+    ok = ok && cudaFuncSetAttribute(ssm_scan_kernel<TI, 64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) == cudaSuccess;
+    ok = ok && cudaFuncSetAttribute(ssm_scan_kernel<TI, 64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) == cudaSuccess;
+    if (!ok) {
+      once.forget();
+      return fail("ssm_scan: cannot reserve %d bytes of shared memory", most);
+    }
+  }
   if (NPER == 16) {
     if (local) ilb::launch(ssm_scan_kernel<TI, 16, true>, grid, block, smem, stream, p);
     else ilb::launch(ssm_scan_kernel<TI, 16, false>, grid, block, smem, stream, p);
@@ -347,16 +376,6 @@ static int scan_launch(const ScanParams& p, int n_blocks, cudaStream_t stream) {
     if (local) ilb::launch(ssm_scan_kernel<TI, 32, true>, grid, block, smem, stream, p);
     else ilb::launch(ssm_scan_kernel<TI, 32, false>, grid, block, smem, stream, p);
   } else {
-    // four threads a column (a state of up to 256 rows) need more than the default 48 KB: ask once for the most
-    static OncePerDevice once;
-    constexpr size_t kMost = sizeof(float) * ((size_t)2 * kScanTokens * 256 + kScanTokens * kScanCols + 2 * kScanTokens + 4 +
-                                             (size_t)kScanTokens * 4 * kScanCols);
-    if (once.first() &&
-        (cudaFuncSetAttribute(ssm_scan_kernel<TI, 64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMost) != cudaSuccess ||
-         cudaFuncSetAttribute(ssm_scan_kernel<TI, 64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMost) != cudaSuccess)) {
-      once.forget();
-      return fail("ssm_scan: cannot reserve %zu bytes of shared memory", kMost);
-    }
     if (local) ilb::launch(ssm_scan_kernel<TI, 64, true>, grid, block, smem, stream, p);
     else ilb::launch(ssm_scan_kernel<TI, 64, false>, grid, block, smem, stream, p);
   }
