@@ -77,7 +77,19 @@ CONFIG_X = model(1000, 256, 1e-6, [
     layer(latent(4, 64, 32, 128, 0.12, window=100), moe(1, 1, 128, 3.0)),
     layer(latent(8, 32, 64, 64, 0.17), None),
 ], bigram=(509, 3, 11), loop=(1, 3, 2))
-CASES = {"U": (CONFIG_U, 21, 4), "V": (CONFIG_V, 22, 16), "W": (CONFIG_W, 23, 8), "X": (CONFIG_X, 24, 16)}     # config, seed, page size
+# Y: sizes that are multiples of nothing: width 100, heads of 5 with a state of 7, a latent of 9 with keys of 5 and
+# values of 7, experts of 11; the loop covers every layer and runs once.
+CONFIG_Y = model(101, 100, 1e-5, [
+    layer(ssd(3, 5, 7, 3, 3, 1), moe(3, 2, 11, 1.25)),
+    layer(latent(3, 5, 7, 9, 0.45, window=3), None),
+    layer(ssd(2, 9, 33, 1, 7, 2), None),
+], bigram=(10, 3, 1), loop=(0, 3, 1), logit_scale=3.0)
+# Z: recurrences only: the model has no pages at all, only state slots.
+CONFIG_Z = model(150, 64, 1e-5, [
+    layer(ssd(4, 16, 32, 2, 4, 2), moe(4, 2, 32, 2.0)),
+    layer(ssd(2, 32, 64, 1, 2, 1), None),
+], bigram=(31, 5, 7))
+CASES = {"Y": (CONFIG_Y, 25, 4), "Z": (CONFIG_Z, 26, 16), "U": (CONFIG_U, 21, 4), "V": (CONFIG_V, 22, 16), "W": (CONFIG_W, 23, 8), "X": (CONFIG_X, 24, 16)}     # config, seed, page size
 
 _FOLDERS: Dict[tuple, str] = {}
 _PLAIN: Dict[tuple, "Plain"] = {}

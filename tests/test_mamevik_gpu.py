@@ -2,7 +2,8 @@
 64-bit statement in plain_mamevik.py.  The configurations are in mamevik_cases.py: U (odd sizes, exact
 kernels, a loop from the first layer), V (the tensor-core kernels' sizes, a loop in the middle that runs
 three times), W (no loop, no table of pairs, a state of 200 rows, one tap, a window of one token), X (V's sizes
-with every expert chosen, for long bfloat16 prompts whose routing must not flip).
+with every expert chosen, for long bfloat16 prompts whose routing must not flip), Y (sizes that are multiples of
+nothing, a loop over all layers that runs once), Z (recurrences only: no pages, only state slots).
 """
 import json
 import math
@@ -20,7 +21,8 @@ from helpers import ROOT, Trace, assert_close, check_trace, random_tokens, run_t
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
-ENGINE_CASES = [("U", "float32"), ("U", "bfloat16"), ("V", "float32"), ("V", "bfloat16"), ("W", "float32"), ("W", "bfloat16")]
+ENGINE_CASES = [("U", "float32"), ("U", "bfloat16"), ("V", "float32"), ("V", "bfloat16"), ("W", "float32"), ("W", "bfloat16"),
+                ("Y", "float32"), ("Y", "bfloat16"), ("Z", "float32"), ("Z", "bfloat16")]
 
 
 @pytest.fixture(scope="module")
