@@ -417,7 +417,32 @@ ILB_EXPORT int ilb_ssm_scan(const float* act, const void* proj, int dtype, int l
 }
 
 // ---------------------------------------------------------------- gate and grouped norm
-template <typename TI, typename TO>
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+  __device__ static __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  __device__ static __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<__nv_bfloat16> {
+  __device__ static __forceinline__ float4 load(const __nv_bfloat16* p) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    return make_float4(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xFFFF0000u), __uint_as_float(r.y << 16),
+                       __uint_as_float(r.y & 0xFFFF0000u));
+  }
+  __device__ static __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = pk;
+  }
+};
+
+// One block per (token, part).  VEC: the part's length is a multiple of 4 and every row starts on a 16-byte (8-byte for
+// bfloat16) boundary: four elements an access, and up to kGateKeep vectors a thread stay in registers between the sum
+// and the write, so that y and the gate are read once.
+constexpr int kGateKeep = 4;
+
+template <typename TI, typename TO, bool VEC>
 __global__ void __launch_bounds__(256)
 gated_group_norm_kernel(const float* __restrict__ y, const TI* __restrict__ gate, int ld_gate, const float* __restrict__ w,
                         TO* __restrict__ out, int width, int groups, float eps) {
@@ -427,16 +452,52 @@ gated_group_norm_kernel(const float* __restrict__ y, const TI* __restrict__ gate
   const int t = blockIdx.x, part = blockIdx.y, n = width / groups;
   const float* yr = y + (size_t)t * width + (size_t)part * n;
   const TI* zr = gate + (size_t)t * ld_gate + (size_t)part * n;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float v = yr[i] * silu_f(to_float(zr[i]));
-    ss = fmaf(v, v, ss);
-  }
-  ss = block_sum(ss, scratch);
-  const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+  const float* wr = w + (size_t)part * n;
   TO* o = out + (size_t)t * width + (size_t)part * n;
-  for (int i = threadIdx.x; i < n; i += blockDim.x)
-    o[i] = from_float<TO>(yr[i] * silu_f(to_float(zr[i])) * inv * w[(size_t)part * n + i]);
+  float ss = 0.f;
+  if constexpr (VEC) {
+    float4 keep[kGateKeep];
+    const int n4 = n / 4;
+#pragma unroll
+    for (int j = 0; j < kGateKeep; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < n4) {
+        const float4 a = Vec4<float>::load(yr + 4 * i), z = Vec4<TI>::load(zr + 4 * i);
+        keep[j] = make_float4(a.x * silu_f(z.x), a.y * silu_f(z.y), a.z * silu_f(z.z), a.w * silu_f(z.w));
+        ss = fmaf(keep[j].x, keep[j].x, ss); ss = fmaf(keep[j].y, keep[j].y, ss);
+        ss = fmaf(keep[j].z, keep[j].z, ss); ss = fmaf(keep[j].w, keep[j].w, ss);
+      }
+    }
+    for (int i = threadIdx.x + kGateKeep * blockDim.x; i < n4; i += blockDim.x) {
+      const float4 a = Vec4<float>::load(yr + 4 * i), z = Vec4<TI>::load(zr + 4 * i);
+      const float v0 = a.x * silu_f(z.x), v1 = a.y * silu_f(z.y), v2 = a.z * silu_f(z.z), v3 = a.w * silu_f(z.w);
+      ss = fmaf(v0, v0, ss); ss = fmaf(v1, v1, ss); ss = fmaf(v2, v2, ss); ss = fmaf(v3, v3, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+#pragma unroll
+    for (int j = 0; j < kGateKeep; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < n4) {
+        const float4 g = Vec4<float>::load(wr + 4 * i);
+        Vec4<TO>::store(o + 4 * i, make_float4(keep[j].x * inv * g.x, keep[j].y * inv * g.y, keep[j].z * inv * g.z, keep[j].w * inv * g.w));
+      }
+    }
+    for (int i = threadIdx.x + kGateKeep * blockDim.x; i < n4; i += blockDim.x) {
+      const float4 a = Vec4<float>::load(yr + 4 * i), z = Vec4<TI>::load(zr + 4 * i), g = Vec4<float>::load(wr + 4 * i);
+      Vec4<TO>::store(o + 4 * i, make_float4(a.x * silu_f(z.x) * inv * g.x, a.y * silu_f(z.y) * inv * g.y,
+                                             a.z * silu_f(z.z) * inv * g.z, a.w * silu_f(z.w) * inv * g.w));
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const float v = yr[i] * silu_f(to_float(zr[i]));
+      ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+      o[i] = from_float<TO>(yr[i] * silu_f(to_float(zr[i])) * inv * wr[i]);
+  }
 }
 
 // out[t, :] = rms over each of `groups` equal parts of (y[t, :] * silu(gate[t, :])) * w; gate is [T, ld_gate] of
@@ -447,15 +508,17 @@ ILB_EXPORT int ilb_gated_group_norm(const float* y, const void* gate, int dtype,
   ILB_REQUIRE(eps > 0.f, "gated_group_norm: eps must be positive");
   if (rows == 0) return 0;
   const int n = width / groups;
-  const int threads = n >= 1024 ? 256 : (n >= 256 ? 128 : 64);
-  if (dtype == kF32)
-    ilb::launch(gated_group_norm_kernel<float, float>, dim3(rows, groups), dim3(threads), 0, stream, y, (const float*)gate, ld_gate, w,
-                (float*)out, width, groups, eps);
-  else if (dtype == kBF16)
-    ilb::launch(gated_group_norm_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(rows, groups), dim3(threads), 0, stream, y,
-                (const __nv_bfloat16*)gate, ld_gate, w, (__nv_bfloat16*)out, width, groups, eps);
-  else
-    return fail("gated_group_norm: unknown dtype %d", dtype);
+  const size_t esize = dtype == kF32 ? 4 : 2;
+  const bool vec = n % 4 == 0 && width % 4 == 0 && ld_gate % 4 == 0 && ((uintptr_t)y % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
+                   ((uintptr_t)gate % (4 * esize) == 0) && ((uintptr_t)out % (4 * esize) == 0);
+  const int per = vec ? n / 4 : n;
+  const int threads = per >= 1024 ? 256 : (per >= 256 ? 128 : 64);
+#define ILB_GN(TI, VEC) ilb::launch(gated_group_norm_kernel<TI, TI, VEC>, dim3(rows, groups), dim3(threads), 0, stream, y, (const TI*)gate, \
+                                     ld_gate, w, (TI*)out, width, groups, eps)
+  if (dtype == kF32) { if (vec) ILB_GN(float, true); else ILB_GN(float, false); }
+  else if (dtype == kBF16) { if (vec) ILB_GN(__nv_bfloat16, true); else ILB_GN(__nv_bfloat16, false); }
+  else return fail("gated_group_norm: unknown dtype %d", dtype);
+#undef ILB_GN
   return check_launch("gated_group_norm");
 }
 

@@ -380,14 +380,15 @@ def test_recurrence_in_one_pass_in_chunks_and_in_portions(heads, P, N, groups):
         assert float(state[1].min()) == 5.0
 
 
-@pytest.mark.parametrize("width,groups", [(48, 1), (96, 3), (512, 2), (4096, 1)])
+@pytest.mark.parametrize("width,groups", [(48, 1), (96, 3), (512, 2), (4096, 1), (8192, 1)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_gate_and_grouped_norm(width, groups, dtype):
+@pytest.mark.parametrize("pad", [9, 8])          # rows of the gate on odd and on 16-byte boundaries (the four-element accesses)
+def test_gate_and_grouped_norm(width, groups, dtype, pad):
     from inferloop_b200.csrc import ops
     g = torch.Generator().manual_seed(width + groups)
     T = 7
     y = torch.randn(T, width, generator=g)
-    z = torch.randn(T, width + 9, generator=g).to(dtype)
+    z = torch.randn(T, width + pad, generator=g).to(dtype)
     w = 1 + 0.1 * torch.randn(width, generator=g)
     out = torch.empty(T, width, dtype=dtype, device=DEV)
     ops.gated_group_norm(f32(y), z.to(DEV), f32(w), 1e-5, groups, out)
