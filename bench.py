@@ -755,8 +755,8 @@ def mamevik_config(kind: str, layers: int, width: int, vocab: int, experts: int,
     mlp = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff, "limit": 7.0}}
     pick = {"latent": lambda i: latent, "ssd": lambda i: ssd, "mixed": lambda i: ssd if i % 2 else latent}[kind]
     cfg = {"architecture": "Mamevik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
-           "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
-           "layers": [dict(pick(i), mlp=dict(mlp)) for i in range(layers)], "logit_scale": 1.0, "logit_softcap": 30.0}
+           "embedding": {"bigram": {"buckets": 65521, "mul_prev": 131, "mul_cur": 17}},
+           "layers": [dict(pick(i), mlp=dict(mlp)) for i in range(layers)], "logit_scale": 1.0, "logit_softcap": 50.0}
     if kind == "mixed":
         cfg["loop"] = {"start": layers // 2 - 1, "stop": layers // 2 + 1, "times": 2}
     return cfg

@@ -55,18 +55,18 @@ CONFIG_U = model(211, 72, 3e-5, [
 ], bigram=(97, 13, 5), loop=(0, 2, 2), logit_scale=2.0, logit_softcap=10.0)
 # V: the sizes the tensor-core kernels take: latents of 64 and 128 elements (the mma.sync attention), experts
 # of 64 (the grouped tcgen05 product with the gated unit in its epilogue), a state of 128 rows (two threads a
-# column), widths in multiples of 64; a loop in the middle that runs three times; no cap on the logits.
+# column), widths in multiples of 64; a loop over the last two layers that runs three times; no cap on the logits.
 CONFIG_V = model(1000, 256, 1e-6, [
     layer(latent(8, 32, 64, 64, 0.17, window=33), moe(6, 2, 64, 7.0)),
     layer(ssd(8, 64, 128, 2, 4, 1), moe(6, 2, 64, 7.0)),
     layer(latent(4, 64, 32, 128, 0.12, window=100), moe(3, 1, 128, 3.0)),
     layer(latent(8, 32, 64, 64, 0.17, window=33), None),
-], bigram=(509, 3, 11), loop=(1, 3, 3))
+], bigram=(509, 3, 11), loop=(2, 4, 3))
 # W: no loop and no table of pairs; a state of 200 rows (four threads a column, the large shared memory), heads of
 # 80 (two column tiles), a convolution of one tap and one of five; a latent of 96; a window of one token.
 CONFIG_W = model(300, 128, 1e-5, [
     layer(ssd(2, 80, 200, 1, 1, 2), None),
-    layer(latent(4, 16, 16, 96, 0.25, window=1), moe(4, 2, 32, 1.5)),
+    layer(latent(5, 16, 16, 96, 0.25, window=1), moe(4, 2, 32, 1.75)),
     layer(ssd(4, 16, 24, 2, 5, 4), None),
     layer(latent(2, 48, 24, 96, 0.2, window=19), None),
 ], logit_scale=0.25, logit_softcap=5.0)

@@ -22,7 +22,7 @@ def test_the_run_order_repeats_the_looped_layers_with_a_cache_per_run():
     spec = spec_of(cases.CONFIG_V)
     n = len(cases.CONFIG_V["layers"])
     order = [(e.layer, e.instance) for e in spec.run_order]
-    assert order == [(0, 0)] + [x for p in range(3) for x in ((n, p), (1, p), (2, p))] + [(3, 0)]
+    assert order == [(0, 0), (1, 0)] + [x for p in range(3) for x in ((n, p), (2, p), (3, p))]       # the loop reaches the last layer
     assert spec.layers[n].block.kind == "loop_input" and spec.head_name is None and spec.logits_post is None
     u = spec_of(cases.CONFIG_U)
     assert [(e.layer, e.instance) for e in u.run_order][:3] == [(4, 0), (0, 0), (1, 0)]          # the loop starts at the first layer
@@ -90,11 +90,13 @@ def test_every_run_of_a_looped_layer_has_pages_and_state_of_its_own():
     assert needs[2].paged.head_dim == 128 and needs[2].paged.kv_heads == 1 and needs[2].paged.window == 100 and needs[2].paged.value_dim == 0
     assert model.model_slot_needs() == (SlotStateNeed("previous_token", (), torch.int32),)
     m = CacheManager(needs, page_size=16, num_pages=8, max_requests=2, run_order=spec.run_order, model_slots=model.model_slot_needs())
-    # layers 0 and 3 share a group (one latent of 64, window 33); layer 2 has three caches of its own group
+    # layer 0 and the three runs of layer 3 share a group (one latent of 64, window 33); layer 2 has three caches of its own group
     by_need = {(g.need.head_dim, g.need.window): g.layers for g in m.groups}
-    assert by_need == {(64, 33): [0, 3], (128, 100): [2, 2, 2]}
+    assert by_need == {(64, 33): [0, 3, 3, 3], (128, 100): [2, 2, 2]}
     caches = [m.layer_cache(e) for e in spec.run_order]
-    assert [c.instance for c in caches] == [0, 0, 0, 0, 1, 1, 1, 2, 2, 2, 0]
+    assert [c.instance for c in caches] == [0, 0, 0, 0, 0, 1, 1, 1, 2, 2, 2]
+    k = [c.k for c in caches]
+    assert m.groups[0].layers == [0, 3, 3, 3] and all(x is None for x in k)        # (no device: the ledger alone)
     m.begin("a"); m.ensure("a", 40); m.commit("a", 40)
     assert m.pages_needed("a", 41) == {0: 0, 1: 0}
     m.release("a")
