@@ -48,7 +48,7 @@ def tokens_for(root, name, dtype, n, seed):
     key = (name, dtype, n, seed)
     if key not in _TOKENS:
         model = cases.plain_model(root, name, stored(dtype))
-        _TOKENS[key] = cases.decided_tokens(model, n, cases.CASES[name][0]["vocab"], seed, 2e-2 if dtype == "bfloat16" else 1e-4)
+        _TOKENS[key] = cases.decided_tokens(model, n, cases.CASES[name][0]["vocab"], seed, 3e-2 if dtype == "bfloat16" else 1e-4)
     return _TOKENS[key]
 
 
