@@ -410,7 +410,8 @@ def _paged(c, page_size, pages_total, order):
 
 @pytest.mark.parametrize("dtype,rank,heads,window", [
     (torch.float32, 24, 3, 7), (torch.float32, 300, 2, None), (torch.bfloat16, 64, 8, 33), (torch.bfloat16, 96, 5, 37),
-    (torch.bfloat16, 128, 16, 100), (torch.bfloat16, 128, 5, None), (torch.bfloat16, 40, 2, 5)])
+    (torch.bfloat16, 128, 16, 100), (torch.bfloat16, 128, 5, None), (torch.bfloat16, 40, 2, 5), (torch.bfloat16, 32, 4, 20), (torch.bfloat16, 64, 20, 50),
+    (torch.bfloat16, 96, 17, None), (torch.float32, 128, 2, 300)])
 def test_attention_with_a_sink_and_a_window_over_cached_latents(dtype, rank, heads, window):
     """Keys and values are the same cached vectors; the softmax's denominator holds a sink per head.  Prompt
     portions and single tokens; pages out of order; a key that stands out sits just inside the window of one
