@@ -169,7 +169,7 @@ def cmd_inspect(args) -> int:
                       "layers": [{"prefix": l.prefix, "block": l.block.kind, "mixer": l.mixer.kind,
                                   "feed_forward": l.feed_forward.kind, "norm": l.norm.kind,
                                   "window": l.mixer.get("window")} for l in spec.layers],
-                      "run_order": [[e.layer, e.cache_of] for e in spec.run_order]}, indent=2))
+                      "run_order": [[e.layer, e.cache_of] + ([e.instance] if e.instance else []) for e in spec.run_order]}, indent=2))      # (layer, cache owner, run of a looped layer)
     return 0
 
 
