@@ -17,15 +17,22 @@
 
 using namespace ilb;
 
+struct LatentWrite {
+  const float* w; float eps;
+  const int* positions; const int* seq_of_token; const int* block_table;
+  int col0, rank, max_blocks, page_size, num_pages;
+};
+
+// One block of 128 threads writes the latent of token t.
 template <typename TI, typename TC>
-__global__ void __launch_bounds__(128)
-latent_write_kernel(const TI* __restrict__ proj, int ld, int col0, int rank, const float* __restrict__ w, float eps,
-                    const int* __restrict__ positions, const int* __restrict__ seq_of_token,
-                    const int* __restrict__ block_table, int max_blocks, int page_size, int num_pages, TC* __restrict__ cache) {
-  ilb::pdl_launch_dependents();
-  ilb::pdl_wait();
-  __shared__ float scratch[33];
-  const int t = blockIdx.x;
+__device__ __forceinline__ void latent_write_token(const TI* __restrict__ proj, int ld, const LatentWrite& a, TC* __restrict__ cache,
+                                                   int t, float* scratch) {
+  const int col0 = a.col0, rank = a.rank, max_blocks = a.max_blocks, page_size = a.page_size, num_pages = a.num_pages;
+  const float* w = a.w;
+  const float eps = a.eps;
+  const int* positions = a.positions;
+  const int* seq_of_token = a.seq_of_token;
+  const int* block_table = a.block_table;
   const TI* row = proj + (size_t)t * ld + col0;
   float ss = 0.f;
   for (int i = threadIdx.x; i < rank; i += blockDim.x) {
@@ -42,14 +49,23 @@ latent_write_kernel(const TI* __restrict__ proj, int ld, int col0, int rank, con
     dst[i] = from_float<TC>(to_float(row[i]) * inv * w[i]);
 }
 
+template <typename TI, typename TC>
+__global__ void __launch_bounds__(128)
+latent_write_kernel(const TI* __restrict__ proj, int ld, const LatentWrite a, TC* __restrict__ cache) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  __shared__ float scratch[33];
+  latent_write_token<TI, TC>(proj, ld, a, cache, blockIdx.x, scratch);
+}
+
 ILB_EXPORT int ilb_latent_write(const void* proj, int dtype, int ld, int col0, int rank, const float* w, float eps,
                                 const int* positions, const int* seq_of_token, const int* block_table, int max_blocks,
                                 int page_size, int num_pages, void* cache, int cache_dtype, int n_tokens, cudaStream_t stream) {
   ILB_REQUIRE(rank > 0 && ld >= col0 + rank && n_tokens >= 0 && eps > 0.f, "latent_write: bad sizes");
   ILB_REQUIRE(page_size > 0 && max_blocks > 0 && num_pages > 0, "latent_write: bad cache geometry");
   if (n_tokens == 0) return 0;
-#define ILB_LW(TI, TC) ilb::launch(latent_write_kernel<TI, TC>, dim3(n_tokens), dim3(128), 0, stream, (const TI*)proj, ld, col0, rank, w, \
-                                    eps, positions, seq_of_token, block_table, max_blocks, page_size, num_pages, (TC*)cache)
+  const LatentWrite a{w, eps, positions, seq_of_token, block_table, col0, rank, max_blocks, page_size, num_pages};
+#define ILB_LW(TI, TC) ilb::launch(latent_write_kernel<TI, TC>, dim3(n_tokens), dim3(128), 0, stream, (const TI*)proj, ld, a, (TC*)cache)
   if (dtype == kF32 && cache_dtype == kF32) ILB_LW(float, float);
   else if (dtype == kBF16 && cache_dtype == kBF16) ILB_LW(__nv_bfloat16, __nv_bfloat16);
   else if (dtype == kBF16 && cache_dtype == kF32) ILB_LW(__nv_bfloat16, float);
@@ -64,14 +80,9 @@ constexpr int kHeadTokens = 16;
 // Block (128 / KS columns n) x (KS ranges of k).  Many tokens: KS = 1, a thread owns a column for 16 tokens.  A step
 // of few tokens has few blocks of that kind, so its k range is cut in four and the parts meet in shared memory.
 template <typename TI, typename TW, typename TO, int KS>
-__global__ void __launch_bounds__(128)
-head_matmul_kernel(const TI* __restrict__ x, int ldx, const TW* __restrict__ w, TO* __restrict__ out, int ldo,
-                   int n_tokens, int K, int N) {
-  ilb::pdl_launch_dependents();
-  ilb::pdl_wait();
+__device__ __forceinline__ void head_matmul_block(const TI* __restrict__ x, int ldx, const TW* __restrict__ w, TO* __restrict__ out,
+                                                  int ldo, int n_tokens, int K, int N, int t0, int h, int n_block, float* xs) {
   constexpr int NT = 128 / KS;
-  extern __shared__ __align__(16) float xs[];           // [kHeadTokens][K], then (KS > 1) [KS][kHeadTokens][NT]
-  const int t0 = blockIdx.x * kHeadTokens, h = blockIdx.y;
   const int ts = min(kHeadTokens, n_tokens - t0);
   for (int i = threadIdx.x; i < kHeadTokens * K; i += 128) {
     const int tt = i / K, k = i % K;
@@ -79,7 +90,7 @@ head_matmul_kernel(const TI* __restrict__ x, int ldx, const TW* __restrict__ w, 
   }
   __syncthreads();
   const int tn = threadIdx.x % NT, tk = threadIdx.x / NT;
-  const int n = blockIdx.z * NT + tn;
+  const int n = n_block * NT + tn;
   const bool live = n < N;
   const int per = ((K + KS - 1) / KS + 3) / 4 * 4;
   const int k0 = tk * per, k1 = min(K, k0 + per);
@@ -122,6 +133,36 @@ head_matmul_kernel(const TI* __restrict__ x, int ldx, const TW* __restrict__ w, 
 #pragma unroll
   for (int tt = 0; tt < kHeadTokens; ++tt)
     if (tt < ts) out[(size_t)(t0 + tt) * ldo + (size_t)h * N + n] = from_float<TO>(acc[tt]);
+}
+
+template <typename TI, typename TW, typename TO, int KS>
+__global__ void __launch_bounds__(128)
+head_matmul_kernel(const TI* __restrict__ x, int ldx, const TW* __restrict__ w, TO* __restrict__ out, int ldo,
+                   int n_tokens, int K, int N) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  extern __shared__ __align__(16) float xs[];           // [kHeadTokens][K], then (KS > 1) [KS][kHeadTokens][NT]
+  head_matmul_block<TI, TW, TO, KS>(x, ldx, w, out, ldo, n_tokens, K, N, blockIdx.x * kHeadTokens, blockIdx.y, blockIdx.z, xs);
+}
+
+// The input stage of a step of few tokens in one launch: blocks (tile of 16 tokens, head, 32 columns) map the queries
+// to the latent space, and sixteen more blocks a tile write the latents of its tokens.
+template <typename TI, typename TC, typename TO>
+__global__ void __launch_bounds__(128)
+latent_input_kernel(const TI* __restrict__ proj, int ld, const TI* __restrict__ w, TO* __restrict__ q_out, int ldo, int n_tokens,
+                    int heads, int K, int N, const LatentWrite a, TC* __restrict__ cache) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  extern __shared__ __align__(16) float xs[];
+  __shared__ float scratch[33];
+  const int n_blocks = (N + 31) / 32, t0 = blockIdx.x * kHeadTokens;
+  const int y = blockIdx.y;
+  if (y < heads * n_blocks) {
+    head_matmul_block<TI, TI, TO, 4>(proj, ld, w, q_out, ldo, n_tokens, K, N, t0, y / n_blocks, y % n_blocks, xs);
+  } else {
+    const int t = t0 + (y - heads * n_blocks);
+    if (t < n_tokens) latent_write_token<TI, TC>(proj, ld, a, cache, t, scratch);
+  }
 }
 
 // The same product for many bfloat16 tokens on the tensor cores (mma.sync m16n8k16, 32-bit sums): a block of four
@@ -217,6 +258,30 @@ ILB_EXPORT int ilb_head_matmul(const void* x, int dtype, int ldx, const void* w,
   else return fail("head_matmul: unsupported dtypes %d/%d", dtype, out_dtype);
 #undef ILB_HM
   return check_launch("head_matmul");
+}
+
+// ilb_latent_write and ilb_head_matmul (queries: heads x K at the row's start) of a step of few tokens as one launch.
+ILB_EXPORT int ilb_latent_input(const void* proj, int dtype, int ld, const void* w, void* q_out, int out_dtype, int ldo, int n_tokens,
+                                int heads, int K, int N, int col0, int rank, const float* norm_w, float eps, const int* positions,
+                                const int* seq_of_token, const int* block_table, int max_blocks, int page_size, int num_pages,
+                                void* cache, int cache_dtype, cudaStream_t stream) {
+  ILB_REQUIRE(n_tokens >= 0 && heads > 0 && K > 0 && N > 0 && rank > 0 && eps > 0.f, "latent_input: bad sizes");
+  ILB_REQUIRE(ld >= heads * K && ld >= col0 + rank && ldo >= heads * N, "latent_input: strides too small");
+  ILB_REQUIRE(page_size > 0 && max_blocks > 0 && num_pages > 0, "latent_input: bad cache geometry");
+  const size_t smem = sizeof(float) * kHeadTokens * ((size_t)K + 128);
+  ILB_REQUIRE(smem <= 48 * 1024, "latent_input: inner size %d exceeds %d", K, 48 * 1024 / 4 / kHeadTokens - 128);
+  const long long rows = (long long)heads * ((N + 31) / 32) + kHeadTokens;
+  ILB_REQUIRE(rows <= 65535, "latent_input: too many heads");
+  if (n_tokens == 0) return 0;
+  const LatentWrite a{norm_w, eps, positions, seq_of_token, block_table, col0, rank, max_blocks, page_size, num_pages};
+  const dim3 grid((n_tokens + kHeadTokens - 1) / kHeadTokens, (unsigned)rows);
+#define ILB_LI(TI, TC, TO) ilb::launch(latent_input_kernel<TI, TC, TO>, grid, dim3(128), smem, stream, (const TI*)proj, ld, (const TI*)w, \
+                                        (TO*)q_out, ldo, n_tokens, heads, K, N, a, (TC*)cache)
+  if (dtype == kF32 && cache_dtype == kF32 && out_dtype == kF32) ILB_LI(float, float, float);
+  else if (dtype == kBF16 && cache_dtype == kBF16 && out_dtype == kBF16) ILB_LI(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+  else return fail("latent_input: unsupported dtypes %d/%d/%d", dtype, cache_dtype, out_dtype);
+#undef ILB_LI
+  return check_launch("latent_input");
 }
 
 ILB_DEFINE_LAST_ERROR()

@@ -253,6 +253,25 @@ def latent_write(proj: torch.Tensor, col0: int, rank: int, weight: torch.Tensor,
           _i(cache.shape[0]), _ptr(cache), _i(_code(cache)), _i(proj.shape[0]), _stream(cache))
 
 
+LATENT_INPUT_TOKENS = 16      # steps of up to this many tokens run the latent write and the queries' map as one launch
+
+
+def latent_input(proj: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, col0: int, rank: int, weight: torch.Tensor, eps: float,
+                 step, block_table: torch.Tensor, cache: torch.Tensor) -> None:
+    """`latent_write` and `head_matmul(proj, w, q_out)` of a step of few tokens in one launch (see latent.cu)."""
+    _need(proj, "latent projection"); _need(w, "head_matmul w", proj.dtype); _need(q_out, "mapped queries", proj.dtype)
+    _need(weight, "latent norm weight", torch.float32); _need(cache, "latent cache", proj.dtype); _need(block_table, "block table", torch.int32)
+    heads, K, N = w.shape
+    if cache.dim() != 4 or cache.shape[1] != 1 or cache.shape[3] != rank or weight.numel() != rank:
+        raise KernelError("latent_input: cache must be [pages, 1, page_size, rank]")
+    if proj.shape[0] != step.n_tokens or proj.shape[1] < max(heads * K, col0 + rank) or tuple(q_out.shape) != (proj.shape[0], heads * N):
+        raise KernelError("latent_input: shapes do not agree")
+    _call("latent", "ilb_latent_input", _ptr(proj), _i(_code(proj)), _i(proj.stride(0)), _ptr(w), _ptr(q_out), _i(_code(q_out)),
+          _i(q_out.stride(0)), _i(proj.shape[0]), _i(heads), _i(K), _i(N), _i(col0), _i(rank), _ptr(weight), _f(eps), _ptr(step.positions),
+          _ptr(step.seq_of_token), _ptr(block_table), _i(block_table.shape[1]), _i(cache.shape[2]), _i(cache.shape[0]), _ptr(cache),
+          _i(_code(cache)), _stream(cache))
+
+
 def head_matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out[t, i, :] = x[t, i, :] @ w[i] for every head i; x [T, >= heads * K] (row stride free), w [heads, K, N],
     out [T, heads * N]."""

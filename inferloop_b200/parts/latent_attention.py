@@ -8,7 +8,8 @@
 Only c is cached (one "kv head" of `rank` elements per token, no values beside it).  The engine
 never forms k and v: with q'_i = Uk_i^T q_i the score is q'_i . c_j, and sum_j p_j v_j =
 Uv_i (sum_j p_j c_j), so the attention kernels run over the cached latents as keys and as values
-with all heads sharing them, between two small per-head products (csrc/latent.cu).  A step is the
+with all heads sharing them, between two small per-head products (csrc/latent.cu; a step of up to 16
+tokens writes its latents and maps its queries in one launch).  A step is the
 same computation however its tokens were cut: a prompt's portion and a single token take the same
 path.  W_q and W_dkv are one product.
 """
@@ -85,12 +86,16 @@ class LatentAttention(Mixer):
         ops.scope("attention.qkv_projection")
         linear(x, self.w_in, proj)
         table = step.block_tables[cache.group]
-        ops.scope("attention.latent_norm_cache_write")
-        if cache.writable:
-            ops.latent_write(proj, H * d, r, self.latent_norm, self.eps, step, table, cache.k)
-        ops.scope("attention.queries_to_latent")
         q = ws.buffer("latent.q", (T, H * r), dt)
-        ops.head_matmul(proj, self.up_k, q)
+        if T <= ops.LATENT_INPUT_TOKENS and cache.writable and cache.k.dtype == dt:
+            ops.scope("attention.input_stage (latent norm, cache write, queries to latent)")
+            ops.latent_input(proj, self.up_k, q, H * d, r, self.latent_norm, self.eps, step, table, cache.k)
+        else:
+            ops.scope("attention.latent_norm_cache_write")
+            if cache.writable:
+                ops.latent_write(proj, H * d, r, self.latent_norm, self.eps, step, table, cache.k)
+            ops.scope("attention.queries_to_latent")
+            ops.head_matmul(proj, self.up_k, q)
         ops.scope("attention.attention")
         o = ws.buffer("latent.o", (T, H * r), dt)
         ops.attention(q, o, cache.k, cache.k, step, table, self.window or 0, self.scale, H, 1, r, workspace=ws,

@@ -479,6 +479,18 @@ def test_products_per_head_and_the_latent_write(dtype, heads, K, N):
         got = cache[int(table[seq, pos // page]), 0, pos % page].double().cpu()
         assert (got - want[t]).abs().max() <= (1e-5 if dtype == torch.float32 else 2.0 ** -8 * float(want[t].abs().max()))
     assert float(cache[8].min()) == 7.0
+    # both at once, as steps of few tokens run them: the same latents, the same mapped queries
+    if col0 + rank <= x.shape[1] and col0 >= 0:
+        cache2 = torch.full((12, 1, page, rank), 7.0, dtype=dtype, device=DEV)
+        few = FakeStep([9, 6, 1], [3, 0, 0], [0, 1, -1])
+        q1 = torch.empty(16, heads * N, dtype=dtype, device=DEV)
+        q2 = torch.empty(16, heads * N, dtype=dtype, device=DEV)
+        xd = x[:16].to(DEV)
+        ops.latent_input(xd, w.to(DEV), q1, col0, rank, f32(gw), 1e-5, few, table, cache2)
+        ops.head_matmul(xd, w.to(DEV), q2)
+        cache3 = torch.full((12, 1, page, rank), 7.0, dtype=dtype, device=DEV)
+        ops.latent_write(xd, col0, rank, f32(gw), 1e-5, few, table, cache3)
+        assert torch.equal(q1, q2) and torch.equal(cache2, cache3)
 
 
 @pytest.mark.parametrize("experts,top", [(5, 2), (3, 3), (8, 1), (40, 4)])
